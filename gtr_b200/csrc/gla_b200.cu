@@ -1,0 +1,392 @@
+// Host side of libgla_b200.so: argument checks, tensor-map construction, workspace layout
+// and launches behind the C ABI declared in include/gla_b200.h.  No allocation, no
+// synchronisation on the forward path.
+#include "gla_b200.h"
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "gla_kernel.cuh"
+
+namespace {
+
+thread_local char g_cuda_err[256] = "";
+
+void note_cuda(const char* what, cudaError_t e) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+}
+void note_cu(const char* what, int e) { snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: CUresult %d", what, e); }
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+struct DeviceInfo {
+    bool ok = false;
+    int sms = 0;
+    bool attr_set = false;
+};
+std::mutex g_mu;
+DeviceInfo g_dev[64];
+
+int device_info(int dev, DeviceInfo* out) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceInfo& d = g_dev[dev];
+    if (!d.attr_set) {
+        int major = 0, sms = 0;
+        cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) { note_cuda("cudaDeviceGetAttribute", e); return GLA_B200_ERR_CUDA; }
+        if (major != 10) {
+            snprintf(g_cuda_err, sizeof(g_cuda_err), "device %d has compute capability %d.x, need 10.x", dev, major);
+            return GLA_B200_ERR_DEVICE;
+        }
+        e = cudaFuncSetAttribute(gla::gla_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gla::kSmemBytes);
+        if (e != cudaSuccess) { note_cuda("cudaFuncSetAttribute", e); return GLA_B200_ERR_CUDA; }
+        d.ok = true;
+        d.sms = sms;
+        d.attr_set = true;
+    }
+    *out = d;
+    return GLA_B200_OK;
+}
+
+// ---- workspace layout ------------------------------------------------------------------
+struct WsLayout {
+    size_t ctrl, flags, agg, incl, total;
+    size_t clear_bytes;   // ctrl + flags, zeroed before every launch
+};
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+WsLayout ws_layout(size_t nseq, size_t ns) {
+    WsLayout L;
+    L.ctrl = 0;
+    L.flags = 256;
+    L.clear_bytes = 256 + align_up(nseq * ns * 4, 256);
+    L.agg = L.clear_bytes;
+    L.incl = L.agg + align_up(nseq * ns * gla::kAggStride * 4, 256);
+    L.total = L.incl + align_up(nseq * ns * gla::kD * gla::kD * 4, 256);
+    return L;
+}
+
+constexpr int kMinAutoCps = 4;   // smallest automatic segment length; also sizes the advertised workspace
+
+int num_chunks(int T) { return (T + gla::kChunk - 1) / gla::kChunk; }
+
+// ---- tensor maps ------------------------------------------------------------------------
+struct MapKey {
+    const void* ptr[gla::kNumTensors];
+    int64_t stride[gla::kNumTensors][3];
+    int B, T, H, Hc, Wc, col;
+    int dev;
+    bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapEntry {
+    MapKey key;
+    gla::Maps maps;
+};
+std::vector<MapEntry> g_map_cache;
+constexpr size_t kMapCacheMax = 64;
+
+int build_maps(const MapKey& key, gla::Maps* out) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) {
+        snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled is not available from this driver");
+        return GLA_B200_ERR_DEVICE;
+    }
+    for (int t = 0; t < gla::kNumTensors; ++t) {
+        if (key.ptr[t] == nullptr) continue;
+        const int64_t sb = key.stride[t][0], st = key.stride[t][1], sh = key.stride[t][2];
+        // dims: (d, head, row-in-column, column, batch)
+        const cuuint64_t gdim[5] = {static_cast<cuuint64_t>(gla::kD), static_cast<cuuint64_t>(key.H),
+                                    static_cast<cuuint64_t>(key.Hc), static_cast<cuuint64_t>(key.Wc),
+                                    static_cast<cuuint64_t>(key.B)};
+        const int64_t row_stride = key.col ? st * key.Wc : st;
+        const int64_t col_stride = key.col ? st : st * key.T;
+        const cuuint64_t gstr[4] = {static_cast<cuuint64_t>(sh) * 2, static_cast<cuuint64_t>(row_stride) * 2,
+                                    static_cast<cuuint64_t>(col_stride) * 2, static_cast<cuuint64_t>(sb) * 2};
+        const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        for (int b = 0; b < gla::kNumBoxes; ++b) {
+            const cuuint32_t box[5] = {static_cast<cuuint32_t>(gla::kD), 1, static_cast<cuuint32_t>(64 >> (2 * b)), 1, 1};
+            CUresult r = enc(&out->m[t][b], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(key.ptr[t]), gdim,
+                             gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) { note_cu("cuTensorMapEncodeTiled", static_cast<int>(r)); return GLA_B200_ERR_CUDA; }
+        }
+    }
+    return GLA_B200_OK;
+}
+
+int get_maps(const MapKey& key, gla::Maps* out) {
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        for (const MapEntry& e : g_map_cache)
+            if (e.key == key) { *out = e.maps; return GLA_B200_OK; }
+    }
+    MapEntry e;
+    memset(&e, 0, sizeof(e));
+    e.key = key;
+    int rc = build_maps(key, &e.maps);
+    if (rc != GLA_B200_OK) return rc;
+    *out = e.maps;
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (g_map_cache.size() >= kMapCacheMax) g_map_cache.erase(g_map_cache.begin());
+    g_map_cache.push_back(e);
+    return GLA_B200_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int resolve_strides(const int64_t in[3], int T, int H, int D, int64_t out[3]) {
+    if (in[0] == 0 && in[1] == 0 && in[2] == 0) {
+        out[0] = static_cast<int64_t>(T) * H * D;
+        out[1] = static_cast<int64_t>(H) * D;
+        out[2] = D;
+        return GLA_B200_OK;
+    }
+    for (int i = 0; i < 3; ++i) {
+        if (in[i] <= 0) return GLA_B200_ERR_ARG;
+        if (in[i] % 8 != 0) return GLA_B200_ERR_ALIGN;
+        out[i] = in[i];
+    }
+    if (out[2] < D) return GLA_B200_ERR_ARG;
+    return GLA_B200_OK;
+}
+
+// ---- standalone RMSNorm * w * silu(gate), rows of 64 fp16 --------------------------------
+__global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __half* __restrict__ x, const __half* __restrict__ g,
+                                                            const __half* __restrict__ wgt, __half* __restrict__ y,
+                                                            int64_t rows, float eps) {
+    // 8 lanes per row, 8 fp16 (16 bytes) per lane; a warp covers 4 consecutive rows = 512 contiguous bytes
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
+    const int sub = threadIdx.x & 7;
+    const bool live = row < rows;
+    float xv[8], gv[8], wv[8];
+    uint4 xr = make_uint4(0, 0, 0, 0), gr = xr;
+    const uint4 wr = __ldg(reinterpret_cast<const uint4*>(wgt) + sub);
+    if (live) {
+        xr = __ldg(reinterpret_cast<const uint4*>(x + row * 64) + sub);
+        gr = __ldg(reinterpret_cast<const uint4*>(g + row * 64) + sub);
+    }
+    const uint32_t* xp = &xr.x;
+    const uint32_t* gp = &gr.x;
+    const uint32_t* wp = &wr.x;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 a = gla::unpack_half2(xp[i]), b = gla::unpack_half2(gp[i]), c = gla::unpack_half2(wp[i]);
+        xv[2 * i] = a.x; xv[2 * i + 1] = a.y;
+        gv[2 * i] = b.x; gv[2 * i + 1] = b.y;
+        wv[2 * i] = c.x; wv[2 * i + 1] = c.y;
+        ss += a.x * a.x + a.y * a.y;
+    }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+    const float r = rsqrtf(ss * (1.f / 64.f) + eps);
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float y0 = xv[2 * i] * r * wv[2 * i] * (gv[2 * i] / (1.f + __expf(-gv[2 * i])));
+        const float y1 = xv[2 * i + 1] * r * wv[2 * i + 1] * (gv[2 * i + 1] / (1.f + __expf(-gv[2 * i + 1])));
+        o[i] = gla::pack_half2_sat(y0, y1);
+    }
+    if (live) *(reinterpret_cast<uint4*>(y + row * 64) + sub) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+}  // namespace
+
+extern "C" {
+
+int gla_b200_version(void) { return GLA_B200_VERSION; }
+
+const char* gla_b200_strerror(int code) {
+    switch (code) {
+        case GLA_B200_OK: return "ok";
+        case GLA_B200_ERR_NULL: return "a required pointer is NULL";
+        case GLA_B200_ERR_SHAPE: return "unsupported shape (need K = V = 64, B,T,H >= 0, grid_h*grid_w == T)";
+        case GLA_B200_ERR_ALIGN: return "pointer or stride is not 16-byte aligned";
+        case GLA_B200_ERR_DIRECTION: return "direction must be 0 (row), 1 (row reversed), 2 (column) or 3 (column reversed)";
+        case GLA_B200_ERR_WORKSPACE: return "workspace is NULL, misaligned or smaller than gla_b200_workspace_bytes()";
+        case GLA_B200_ERR_DEVICE: return "the current device is not an sm_100 GPU or the driver lacks tensor-map support";
+        case GLA_B200_ERR_CUDA: return "a CUDA call failed (see gla_b200_last_cuda_error)";
+        case GLA_B200_ERR_TIMEOUT: return "a bounded wait inside the kernel expired; outputs are undefined";
+        case GLA_B200_ERR_ARG: return "invalid argument";
+        default: return "unknown gla_b200 error code";
+    }
+}
+
+const char* gla_b200_last_cuda_error(void) { return g_cuda_err; }
+
+size_t gla_b200_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_t K, int32_t V) {
+    if (B < 0 || T < 0 || H < 0 || K != gla::kD || V != gla::kD) return 0;
+    const size_t nseq = static_cast<size_t>(B) * H;
+    const size_t ns = static_cast<size_t>((num_chunks(T) + kMinAutoCps - 1) / kMinAutoCps);
+    return ws_layout(nseq, ns ? ns : 1).total;
+}
+
+int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
+    if (!a) return GLA_B200_ERR_NULL;
+    if (a->K != gla::kD || a->V != gla::kD || a->B < 0 || a->T < 0 || a->H < 0) return GLA_B200_ERR_SHAPE;
+    if (a->direction < 0 || a->direction > 3) return GLA_B200_ERR_DIRECTION;
+    int gh = a->grid_h, gw = a->grid_w;
+    if (gh == 0 && gw == 0) { gh = 1; gw = a->T; }
+    if (gh < 0 || gw < 0 || static_cast<int64_t>(gh) * gw != a->T) return GLA_B200_ERR_SHAPE;
+    if (a->direction >= 2 && (a->grid_h <= 0 || a->grid_w <= 0)) return GLA_B200_ERR_SHAPE;
+    if (a->scale != a->scale || a->gk_normalizer < 0.f) return GLA_B200_ERR_ARG;
+    const bool gated = a->out_gate != nullptr || a->rms_weight != nullptr;
+    if (gated) return GLA_B200_ERR_ARG;   // fused epilogue: not in this build of the kernel yet
+    if (static_cast<int64_t>(a->B) * a->T * a->H == 0) return GLA_B200_OK;   // nothing to do
+    if (!a->q || !a->k || !a->v || !a->g || !a->o) return GLA_B200_ERR_NULL;
+    if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->g) || !aligned16(a->o) ||
+        (a->initial_state && !aligned16(a->initial_state)) || (a->final_state && !aligned16(a->final_state)))
+        return GLA_B200_ERR_ALIGN;
+    if (a->segments < 0) return GLA_B200_ERR_ARG;
+
+    MapKey key;
+    memset(&key, 0, sizeof(key));
+    const void* ptrs[gla::kNumTensors] = {a->q, a->k, a->g, a->v, a->o, nullptr};
+    const int64_t* strides[gla::kNumTensors] = {a->q_stride, a->k_stride, a->g_stride, a->v_stride, a->o_stride,
+                                                a->gate_stride};
+    int rc = GLA_B200_OK;
+    for (int t = 0; t < gla::kNumTensors; ++t) {
+        key.ptr[t] = ptrs[t];
+        if (!ptrs[t]) continue;
+        rc = resolve_strides(strides[t], a->T, a->H, gla::kD, key.stride[t]);
+        if (rc != GLA_B200_OK) return rc;
+    }
+
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) { note_cuda("cudaGetDevice", ce); return GLA_B200_ERR_CUDA; }
+    if (dev < 0 || dev >= 64) return GLA_B200_ERR_DEVICE;
+    DeviceInfo di;
+    rc = device_info(dev, &di);
+    if (rc != GLA_B200_OK) return rc;
+    const bool col = a->direction >= 2;
+    key.B = a->B; key.T = a->T; key.H = a->H;
+    key.col = col ? 1 : 0;
+    key.Hc = col ? gh : a->T;
+    key.Wc = col ? gw : 1;
+    key.dev = dev;
+
+    // segmentation
+    const int NT = num_chunks(a->T);
+    const int nseq = a->B * a->H;
+    const int slots = 2 * di.sms;
+    int cps;
+    if (a->segments > 0) cps = a->segments;
+    else if (nseq >= slots) cps = NT;
+    else {
+        const long total = static_cast<long>(NT) * nseq;
+        cps = static_cast<int>(total / (3L * slots));
+        if (cps < kMinAutoCps) cps = kMinAutoCps;
+        if (cps > 32) cps = 32;
+    }
+    if (cps > NT) cps = NT;
+    const int NS = (NT + cps - 1) / cps;
+    const WsLayout L = ws_layout(static_cast<size_t>(nseq), static_cast<size_t>(NS));
+    if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < L.total)
+        return GLA_B200_ERR_WORKSPACE;
+
+    gla::Maps maps;
+    rc = get_maps(key, &maps);
+    if (rc != GLA_B200_OK) return rc;
+
+    uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+    gla::Params P;
+    memset(&P, 0, sizeof(P));
+    P.B = a->B; P.T = a->T; P.H = a->H; P.NT = NT;
+    P.Hc = key.Hc; P.Wc = key.Wc;
+    P.rev = a->direction & 1;
+    P.NS = NS; P.cps = cps;
+    P.num_items = nseq * NS;
+    P.gated = 0;
+    P.scale = a->scale;
+    P.inv_norm = a->gk_normalizer > 0.f ? 1.f / a->gk_normalizer : 0.f;
+    P.rms_eps = a->rms_eps;
+    P.rms_w = nullptr;
+    P.s0 = a->initial_state;
+    P.sT = a->final_state;
+    P.ctrl = reinterpret_cast<uint32_t*>(ws + L.ctrl);
+    P.flags = reinterpret_cast<uint32_t*>(ws + L.flags);
+    P.agg = reinterpret_cast<float*>(ws + L.agg);
+    P.incl = reinterpret_cast<float*>(ws + L.incl);
+    P.wait_limit_us = a->wait_limit ? a->wait_limit : 2000000u;
+
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    ce = cudaMemsetAsync(ws, 0, L.clear_bytes, stream);
+    if (ce != cudaSuccess) { note_cuda("cudaMemsetAsync", ce); return GLA_B200_ERR_CUDA; }
+    const int grid = P.num_items < slots ? P.num_items : slots;
+    gla::gla_fwd_kernel<<<grid, gla::kThreads, gla::kSmemBytes, stream>>>(maps, P);
+    ce = cudaPeekAtLastError();
+    if (ce != cudaSuccess) { note_cuda("kernel launch", ce); return GLA_B200_ERR_CUDA; }
+    return GLA_B200_OK;
+}
+
+int gla_b200_check_status(const void* workspace, void* stream) {
+    if (!workspace) return GLA_B200_ERR_NULL;
+    uint32_t ctrl[2] = {0, 0};
+    cudaError_t e = cudaMemcpyAsync(ctrl, workspace, sizeof(ctrl), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) { note_cuda("status read", e); return GLA_B200_ERR_CUDA; }
+    return ctrl[1] == 0 ? GLA_B200_OK : GLA_B200_ERR_TIMEOUT;
+}
+
+int gla_b200_rmsnorm_gated(const void* x, const void* g, const void* w, void* y, int64_t rows, int32_t D, float eps,
+                           void* stream) {
+    if (D != 64 || rows < 0) return GLA_B200_ERR_SHAPE;
+    if (rows == 0) return GLA_B200_OK;
+    if (!x || !g || !w || !y) return GLA_B200_ERR_NULL;
+    if (!aligned16(x) || !aligned16(g) || !aligned16(w) || !aligned16(y)) return GLA_B200_ERR_ALIGN;
+    const int64_t threads = rows * 8;
+    const int64_t blocks = (threads + 255) / 256;
+    if (blocks > 0x7fffffffLL) return GLA_B200_ERR_SHAPE;
+    rmsnorm_gated_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), static_cast<const __half*>(g), static_cast<const __half*>(w),
+        static_cast<__half*>(y), rows, eps);
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) { note_cuda("rmsnorm launch", e); return GLA_B200_ERR_CUDA; }
+    return GLA_B200_OK;
+}
+
+int32_t gla_b200_trt_enqueue(const void* const* inputs, int32_t n_inputs, void* const* outputs, const int64_t* q_dims,
+                             float scale, float gk_normalizer, float rms_eps, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+    if (!inputs || !outputs || !q_dims || !workspace || (n_inputs != 4 && n_inputs != 6)) return -1;
+    gla_b200_args a;
+    memset(&a, 0, sizeof(a));
+    a.q = inputs[0]; a.k = inputs[1]; a.v = inputs[2]; a.g = inputs[3];
+    a.o = outputs[0];
+    const bool fused = n_inputs == 6 && rms_eps > 0.f;
+    if (fused) { a.out_gate = inputs[4]; a.rms_weight = inputs[5]; a.rms_eps = rms_eps; }
+    a.B = static_cast<int32_t>(q_dims[0]); a.T = static_cast<int32_t>(q_dims[1]);
+    a.H = static_cast<int32_t>(q_dims[2]); a.K = static_cast<int32_t>(q_dims[3]);
+    a.V = GLA_B200_HEAD_V;
+    a.scale = scale;
+    a.gk_normalizer = gk_normalizer;
+    // TensorRT hands out workspaces with its own alignment; round up to ours like the reference plugin does
+    uintptr_t p = (reinterpret_cast<uintptr_t>(workspace) + 255u) & ~static_cast<uintptr_t>(255u);
+    const size_t lost = p - reinterpret_cast<uintptr_t>(workspace);
+    if (workspace_bytes < lost) return -1;
+    a.workspace = reinterpret_cast<void*>(p);
+    a.workspace_bytes = workspace_bytes - lost;
+    return gla_b200_forward(&a, stream) == GLA_B200_OK ? 0 : -1;
+}
+
+}  // extern "C"

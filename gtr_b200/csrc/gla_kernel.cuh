@@ -1,0 +1,727 @@
+// Chunkwise gated-linear-attention forward for sm_100a: one persistent kernel.
+//
+// Work decomposition.  A sequence (one batch b, one head h, T tokens along the scan order)
+// is cut into 64-token chunks and the chunks into segments of `cps` chunks.  A work item is
+// one (sequence, segment); CTAs take items from an atomic ticket so that an item's
+// predecessors are always held by CTAs that already run.  For every segment but the last
+// of a sequence the CTA first streams k, g, v only and reduces the segment to an aggregate
+// (decay, state increment), publishes it, obtains its incoming state from its predecessors
+// by a decoupled look-back, and then streams q, k, g, v once more (k, g, v come from L2) to
+// produce the outputs.  Replaces chunk_compute_S_kernel / chunk_scan_*_kernel /
+// chunk_fwd_o_kernel of the reference (engine/gtr/backbone/csrc/gla_chunk.cuh:718-1394).
+//
+// Per chunk, with G the inclusive within-chunk cumulative log gate (fp32), G_m its value at
+// the middle row and G_L at the last row:
+//   qh = q*exp(G)      kh = k*exp(G_L-G)       (fp16, exponents <= 0)
+//   qb = qh*exp(-G_m)  kb = kh*exp(G_m-G_L)    (tf32: fp32 range, exponents within +-64)
+//   A  = tril(qb kb^T)                 tcgen05.mma kind::tf32  -> TMEM
+//   O  = qh S_in + A v                 two tcgen05.mma kind::f16 into one TMEM accumulator
+//   S' = exp(G_L) (.) S_in + kh^T v    tcgen05.mma kind::f16, decay applied in registers (fp32)
+// A chunk whose total decay exceeds e^-64 in any channel takes an exact scalar path for A.
+//
+// Warp roles: warps 0-3 gate math, TMEM epilogues, state; warp 4 TMA producer; warp 5 MMA issue.
+#pragma once
+
+#include "gla_device.cuh"
+
+namespace gla {
+
+constexpr int kChunk = 64;
+constexpr int kD = 64;                    // K = V = 64
+constexpr int kTileBytes = kChunk * 128;  // one fp16 [64 x 64] tile
+constexpr int kStageBytes = 4 * kTileBytes;
+constexpr int kNumStages = 2;
+constexpr int kComputeThreads = 128;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;
+constexpr float kWideLimit = 64.f;        // largest total in-chunk decay (nats) the tf32 path takes
+
+// tensor ids inside Maps
+enum { TQ = 0, TK = 1, TG = 2, TV = 3, TO = 4, TGATE = 5, kNumTensors = 6 };
+constexpr int kNumBoxes = 4;              // box heights 64, 16, 4, 1 rows
+
+struct Maps {
+    CUtensorMap m[kNumTensors][kNumBoxes];
+};
+
+struct Params {
+    int B, T, H, NT;
+    int Hc, Wc;          // column length / number of columns of the scan (row scans: Hc = T, Wc = 1)
+    int rev;             // scan runs from the last token to the first
+    int NS, cps;         // segments per sequence, chunks per segment
+    int num_items;
+    int gated;           // fused RMSNorm * w * silu(gate) epilogue
+    float scale;
+    float inv_norm;      // 1/gk_normalizer, or 0 when g already is a log gate
+    float rms_eps;
+    const __half* rms_w;
+    const float* s0;
+    float* sT;
+    uint32_t* ctrl;      // [0] ticket, [1] status
+    uint32_t* flags;     // per (sequence, segment): 0 none, 1 aggregate, 2 inclusive state
+    float* agg;          // per (sequence, segment): 4096 state increment + 64 log decay
+    float* incl;         // per (sequence, segment): 4096 state after the segment
+    uint32_t wait_limit_us;
+};
+
+constexpr int kAggStride = kD * kD + kD;
+
+// shared memory map (bytes from a 1024-aligned base)
+constexpr int kOffStage = 0;
+constexpr int kOffQbar = kNumStages * kStageBytes;       // 16 KB tf32 (two 8 KB halves)
+constexpr int kOffKbar = kOffQbar + 2 * kTileBytes;
+constexpr int kOffS16 = kOffKbar + 2 * kTileBytes;
+constexpr int kOffMisc = kOffS16 + kTileBytes;
+constexpr int kMiscBytes = 4096;
+constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + alignment slack
+
+struct Misc {
+    uint64_t full[kNumStages];
+    uint64_t empty[kNumStages];
+    uint64_t ops_ready, a_done, a16_ready, o_done, o_free, s_done, s16_ready;
+    uint32_t tmem_base;
+    volatile uint32_t abort;
+    int item;
+    uint32_t wide[2];
+    float tot[2][4][kD];
+    float b4s[2][kD];
+};
+static_assert(sizeof(Misc) <= kMiscBytes, "misc block too large");
+
+enum { WHERE_MBAR = 1, WHERE_LOOKBACK = 2 };
+
+struct Ctx {
+    const Params* p;
+    Misc* misc;
+    uint32_t smem;       // shared address of the 1024-aligned base
+    uint64_t deadline_span_ns;
+};
+
+__device__ __forceinline__ void raise_timeout(const Ctx& c, uint32_t where) {
+    c.misc->abort = 1;
+    atomicCAS(c.p->ctrl + 1, 0u, where);
+}
+
+// Bounded wait.  After a time-out in this CTA every later wait returns at once, so all warps
+// keep following the protocol (arrivals, named barriers) and the CTA drains and exits; the
+// result is then undefined and the status word says so.
+__device__ __forceinline__ void mbar_wait(const Ctx& c, uint64_t* bar, uint32_t parity) {
+    const uint32_t b = smem_u32(bar);
+    if (mbar_try_wait(b, parity)) return;
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+        if (c.misc->abort) return;
+        if (mbar_try_wait(b, parity)) return;
+        if (globaltimer_ns() - t0 > c.deadline_span_ns) {
+            raise_timeout(c, WHERE_MBAR);
+            return;
+        }
+    }
+}
+
+// ---- addressing inside 128-byte-swizzled tiles -------------------------------------------
+__device__ __forceinline__ uint32_t sw_f16(uint32_t row, uint32_t col) {     // col in fp16 elements
+    return row * 128u + ((((col >> 3) ^ row) & 7u) << 4) + ((col & 7u) << 1);
+}
+__device__ __forceinline__ uint32_t sw_f32(uint32_t row, uint32_t col) {     // col in fp32 elements, 0..63
+    const uint32_t c = col & 31u;
+    return (col >> 5) * kTileBytes + row * 128u + ((((c >> 2) ^ row) & 7u) << 4) + ((c & 3u) << 2);
+}
+
+// Enumerate the TMA boxes that cover chunk [p0, p0+64) of the scan.  f(box_id, r, c, smem_row).
+template <class F>
+__device__ __forceinline__ int for_each_box(int p0, int L, int Hc, int rev, F f) {
+    const int u_lo = rev ? (L - p0 - kChunk) : p0;
+    int u0 = max(u_lo, 0);
+    const int u1 = min(u_lo + kChunk, L);
+    const int valid = u1 - u0;
+    while (u0 < u1) {
+        const int c = u0 / Hc;
+        int r = u0 - c * Hc;
+        int len = min(Hc - r, u1 - u0);
+        while (len > 0) {
+            const int id = len >= 64 ? 0 : len >= 16 ? 1 : len >= 4 ? 2 : 3;
+            const int R = 64 >> (2 * id);
+            f(id, r, c, u0 - u_lo);
+            r += R;
+            u0 += R;
+            len -= R;
+        }
+    }
+    return valid;
+}
+
+__device__ __forceinline__ int chunk_valid(int p0, int L) { return min(kChunk, L - p0); }
+
+// ------------------------------------------------------------------------------------------
+// Gate math for one chunk (all 128 compute threads).  Thread (w, l) owns logical rows
+// 16w..16w+15 and channels 2l, 2l+1.  Logical row = position inside the chunk along the scan;
+// physical (shared-memory / TMEM) row is mirrored for reversed scans.
+template <bool kStateOnly>
+__device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, int n, int valid, int w, int l) {
+    const Params& P = *c.p;
+    Misc& M = *c.misc;
+    const uint32_t tq = stage + 0 * kTileBytes, tk = stage + 1 * kTileBytes, tg = stage + 2 * kTileBytes,
+                   tv = stage + 3 * kTileBytes;
+    const uint32_t c0 = 2u * l;
+    const int par = n & 1;
+    const bool rev = P.rev != 0;
+
+    float cs0[16], cs1[16];
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int lam = 16 * w + i;
+        const uint32_t rho = rev ? 63 - lam : lam;
+        float2 gv = make_float2(0.f, 0.f);
+        if (lam < valid) {
+            gv = unpack_half2(ld_shared_u32(tg + sw_f16(rho, c0)));
+            if (P.inv_norm > 0.f) {
+                gv.x = logsigmoid_f(gv.x) * P.inv_norm;
+                gv.y = logsigmoid_f(gv.y) * P.inv_norm;
+            }
+        }
+        a0 += gv.x;
+        a1 += gv.y;
+        cs0[i] = a0;
+        cs1[i] = a1;
+    }
+    M.tot[par][w][c0] = a0;
+    M.tot[par][w][c0 + 1] = a1;
+    named_bar_sync(1, kComputeThreads);
+    float off0 = 0.f, off1 = 0.f, b40 = 0.f, b41 = 0.f, gm0 = 0.f, gm1 = 0.f;
+#pragma unroll
+    for (int ww = 0; ww < 4; ++ww) {
+        const float t0 = M.tot[par][ww][c0], t1 = M.tot[par][ww][c0 + 1];
+        if (ww < w) { off0 += t0; off1 += t1; }
+        if (ww < 2) { gm0 += t0; gm1 += t1; }
+        b40 += t0;
+        b41 += t1;
+    }
+    if (w == 0) {
+        M.b4s[par][c0] = b40;
+        M.b4s[par][c0 + 1] = b41;
+    }
+    bool wide = false;
+    float e10 = 0.f, e11 = 0.f, e20 = 0.f, e21 = 0.f;
+    if (!kStateOnly) {
+        wide = __any_sync(0xffffffffu, (-b40 > kWideLimit) || (-b41 > kWideLimit));
+        if (w == 0 && l == 0) M.wide[par] = wide ? 1u : 0u;
+        if (!wide) {
+            e10 = fast_exp(-gm0);
+            e11 = fast_exp(-gm1);
+            e20 = fast_exp(gm0 - b40);
+            e21 = fast_exp(gm1 - b41);
+        }
+    }
+    const uint32_t qbar = c.smem + kOffQbar, kbar = c.smem + kOffKbar;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int lam = 16 * w + i;
+        const uint32_t rho = rev ? 63 - lam : lam;
+        const uint32_t a16 = sw_f16(rho, c0);
+        if (lam < valid) {
+            const float G0 = off0 + cs0[i], G1 = off1 + cs1[i];
+            const uint32_t kraw = ld_shared_u32(tk + a16);
+            const float2 kv = unpack_half2(kraw);
+            const float kh0 = kv.x * fast_exp(b40 - G0), kh1 = kv.y * fast_exp(b41 - G1);
+            st_shared_u32(tk + a16, pack_half2_sat(kh0, kh1));
+            if (!kStateOnly) {
+                const uint32_t qraw = ld_shared_u32(tq + a16);
+                const float2 qv = unpack_half2(qraw);
+                const float qh0 = qv.x * fast_exp(G0), qh1 = qv.y * fast_exp(G1);
+                st_shared_u32(tq + a16, pack_half2_sat(qh0, qh1));
+                if (!wide) {
+                    const uint32_t a32 = sw_f32(rho, c0);
+                    st_shared_f2(qbar + a32, to_tf32(qh0 * e10), to_tf32(qh1 * e11));
+                    st_shared_f2(kbar + a32, to_tf32(kh0 * e20), to_tf32(kh1 * e21));
+                } else {  // exact path operands, plain layouts: G fp32 [64][64]; raw q, k fp16 [64][64]
+                    st_shared_f2(qbar + rho * 256u + c0 * 4u, G0, G1);
+                    st_shared_u32(kbar + rho * 128u + c0 * 2u, qraw);
+                    st_shared_u32(kbar + kTileBytes + rho * 128u + c0 * 2u, kraw);
+                }
+            }
+        } else {  // beyond the end of the sequence: contributes nothing, and must be finite for the MMAs
+            st_shared_u32(tk + a16, 0u);
+            st_shared_u32(tv + a16, 0u);
+            if (!kStateOnly) {
+                st_shared_u32(tq + a16, 0u);
+                if (!wide) {
+                    const uint32_t a32 = sw_f32(rho, c0);
+                    st_shared_f2(qbar + a32, 0.f, 0.f);
+                    st_shared_f2(kbar + a32, 0.f, 0.f);
+                } else {
+                    st_shared_f2(qbar + rho * 256u + c0 * 4u, b40, b41);
+                    st_shared_u32(kbar + rho * 128u + c0 * 2u, 0u);
+                    st_shared_u32(kbar + kTileBytes + rho * 128u + c0 * 2u, 0u);
+                }
+            }
+        }
+    }
+    fence_proxy_async_smem();
+}
+
+// Exact intra-chunk scores for chunks whose gates are too strong for a common reference:
+// A[i][j] = sum_c q[i][c] k[j][c] exp(G[i][c] - G[j][c]) for j at or before i along the scan.
+__device__ __forceinline__ void exact_scores(const Ctx& c, uint32_t a16_tile, int tid) {
+    const bool rev = c.p->rev != 0;
+    const uint32_t gs = c.smem + kOffQbar, qs = c.smem + kOffKbar, ks = qs + kTileBytes;
+    const uint32_t i = tid >> 1;
+    for (uint32_t j = tid & 1; j < 64; j += 2) {
+        float s = 0.f;
+        const bool keep = rev ? (j >= i) : (j <= i);
+        if (keep) {
+            for (uint32_t ch = 0; ch < 64; ch += 2) {
+                const float2 gi = ld_shared_f2(gs + i * 256u + ch * 4u);
+                const float2 gj = ld_shared_f2(gs + j * 256u + ch * 4u);
+                const float2 qv = unpack_half2(ld_shared_u32(qs + i * 128u + ch * 2u));
+                const float2 kv = unpack_half2(ld_shared_u32(ks + j * 128u + ch * 2u));
+                s += qv.x * kv.x * __expf(gi.x - gj.x);
+                s += qv.y * kv.y * __expf(gi.y - gj.y);
+            }
+        }
+        const __half hv = __float2half_rn(fminf(fmaxf(s, -65504.f), 65504.f));
+        st_shared_u16(a16_tile + sw_f16(i, j), __half_as_ushort(hv));
+    }
+}
+
+// Read this thread's TMEM lane (64 fp32 columns starting at `col`).
+__device__ __forceinline__ void tmem_row64(uint32_t tmem_base, int w, uint32_t col, float* x) {
+    const uint32_t addr = tmem_base + (static_cast<uint32_t>(32 * w) << 16) + col;
+    uint32_t* r = reinterpret_cast<uint32_t*>(x);
+    __syncwarp();   // tcgen05.ld is warp-collective; lane 0 may come from a single-thread branch
+    tmem_ld16(addr, r);
+    tmem_ld16(addr + 16, r + 16);
+    tmem_ld16(addr + 32, r + 32);
+    tmem_ld16(addr + 48, r + 48);
+    tmem_ld_wait();
+}
+
+// Write 64 floats as one fp16 row of a swizzled tile.
+__device__ __forceinline__ void store_row_f16(uint32_t tile, uint32_t row, const float* x) {
+#pragma unroll
+    for (uint32_t m = 0; m < 8; ++m) {
+        const uint32_t a = tile + row * 128u + (((m ^ row) & 7u) << 4);
+        st_shared_v4(a, pack_half2_sat(x[8 * m], x[8 * m + 1]), pack_half2_sat(x[8 * m + 2], x[8 * m + 3]),
+                     pack_half2_sat(x[8 * m + 4], x[8 * m + 5]), pack_half2_sat(x[8 * m + 6], x[8 * m + 7]));
+    }
+}
+
+struct ItemInfo {
+    int seq, seg, b, h, first_chunk, nchunks, state_pass;
+};
+
+__device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
+    ItemInfo it;
+    const int nseq = P.B * P.H;
+    it.seg = item / nseq;
+    it.seq = item - it.seg * nseq;
+    it.b = it.seq / P.H;
+    it.h = it.seq - it.b * P.H;
+    it.first_chunk = it.seg * P.cps;
+    it.nchunks = min(P.cps, P.NT - it.first_chunk);
+    it.state_pass = (it.seg < P.NS - 1) ? 1 : 0;
+    return it;
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params P) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw);
+    Misc& M = *reinterpret_cast<Misc*>(base_ptr + kOffMisc);
+
+    const int tid = threadIdx.x;
+    const int w = tid >> 5, l = tid & 31;
+
+    Ctx ctx;
+    ctx.p = &P;
+    ctx.misc = &M;
+    ctx.smem = base;
+    ctx.deadline_span_ns = static_cast<uint64_t>(P.wait_limit_us) * 1000ull;
+
+    if (tid == 0) {
+        for (int s = 0; s < kNumStages; ++s) {
+            mbar_init(smem_u32(&M.full[s]), 1);
+            mbar_init(smem_u32(&M.empty[s]), 1);
+        }
+        mbar_init(smem_u32(&M.ops_ready), kComputeThreads);
+        mbar_init(smem_u32(&M.a_done), 1);
+        mbar_init(smem_u32(&M.a16_ready), kComputeThreads);
+        mbar_init(smem_u32(&M.o_done), 1);
+        mbar_init(smem_u32(&M.o_free), kComputeThreads);
+        mbar_init(smem_u32(&M.s_done), 1);
+        mbar_init(smem_u32(&M.s16_ready), kComputeThreads);
+        M.abort = 0;
+        fence_mbar_init();
+    }
+    if (w == 4) {
+        tmem_alloc(smem_u32(&M.tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    if (w == 5 && l == 0) {
+        for (int t = 0; t < kNumTensors; ++t)
+            if (t != TGATE || P.gated)
+                tma_prefetch_desc(&maps.m[t][0]);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = M.tmem_base;
+    const uint32_t tmA = tmem + 0, tmO = tmem + 64, tmS = tmem + 128;
+
+    // use counters of every barrier, kept per role (all roles see the same sequence of uses)
+    uint32_t n_full[kNumStages] = {0, 0}, n_empty[kNumStages] = {0, 0};
+    uint32_t n_ops = 0, n_adone = 0, n_a16 = 0, n_odone = 0, n_ofree = 0, n_sdone = 0, n_s16 = 0;
+    uint32_t chunk_ctr = 0;   // chunks processed by this CTA so far: stage = ctr % 2, parity slot = ctr & 1
+
+    float S[kD];              // fp32 state row of channel 16w+l (lanes 0..15 of each compute warp)
+    const bool owner = (w < 4) && (l < 16);
+    const int my_c = 16 * (w & 3) + (l & 15);
+
+    while (true) {
+        if (tid == 0) M.item = static_cast<int>(atomicAdd(P.ctrl, 1u));
+        __syncthreads();
+        const int item = M.item;
+        if (item >= P.num_items) break;
+        const ItemInfo it = decode_item(P, item);
+        const int npass = it.state_pass ? 2 : 1;
+
+        if (w == 4) {
+            // ------------------------------------------------------------ TMA producer
+            if (l == 0) {
+                uint32_t ctr = chunk_ctr;
+                for (int pass = 0; pass < npass; ++pass) {
+                    const bool state_only = it.state_pass && pass == 0;
+                    for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                        const uint32_t s = ctr % kNumStages;
+                        mbar_wait(ctx, &M.empty[s], (n_empty[s]++ & 1u) ^ 1u);
+                        const int p0 = (it.first_chunk + i) * kChunk;
+                        const int valid = chunk_valid(p0, P.T);
+                        const int ntens = state_only ? 3 : 4;
+                        const uint32_t bar = smem_u32(&M.full[s]);
+                        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(valid * 128 * ntens));
+                        const uint32_t stage = base + kOffStage + s * kStageBytes;
+                        for_each_box(p0, P.T, P.Hc, P.rev, [&](int id, int r, int c, int row) {
+                            const uint32_t off = static_cast<uint32_t>(row) * 128u;
+                            if (!state_only)
+                                tma_load_5d(stage + 0 * kTileBytes + off, &maps.m[TQ][id], bar, 0, it.h, r, c, it.b);
+                            tma_load_5d(stage + 1 * kTileBytes + off, &maps.m[TK][id], bar, 0, it.h, r, c, it.b);
+                            tma_load_5d(stage + 2 * kTileBytes + off, &maps.m[TG][id], bar, 0, it.h, r, c, it.b);
+                            tma_load_5d(stage + 3 * kTileBytes + off, &maps.m[TV][id], bar, 0, it.h, r, c, it.b);
+                        });
+                    }
+                }
+            }
+            __syncwarp();
+        } else if (w == 5) {
+            // ------------------------------------------------------------ MMA issue
+            if (l == 0) {
+                constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 64);
+                constexpr uint32_t idO1 = umma_idesc(FMT_F16, 0, 1, 64, 64);
+                constexpr uint32_t idS = umma_idesc(FMT_F16, 1, 1, 64, 64);
+                uint32_t ctr = chunk_ctr;
+                for (int pass = 0; pass < npass; ++pass) {
+                    const bool state_only = it.state_pass && pass == 0;
+                    for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                        const uint32_t s = ctr % kNumStages;
+                        const uint32_t stage = base + kOffStage + s * kStageBytes;
+                        const uint32_t tq = stage, tk = stage + kTileBytes, ta16 = stage + 2 * kTileBytes,
+                                       tv = stage + 3 * kTileBytes;
+                        mbar_wait(ctx, &M.full[s], n_full[s]++ & 1u);
+                        mbar_wait(ctx, &M.ops_ready, n_ops++ & 1u);
+                        tc_fence_after();
+                        if (!state_only) {
+                            if (!M.wide[ctr & 1]) {
+#pragma unroll
+                                for (uint32_t ks = 0; ks < 8; ++ks) {
+                                    const uint32_t o = (ks >> 2) * kTileBytes + (ks & 3) * 32u;
+                                    umma_tf32(tmA, umma_desc_sw128(base + kOffQbar + o),
+                                              umma_desc_sw128(base + kOffKbar + o), idA, ks);
+                                }
+                            }
+                            umma_commit(smem_u32(&M.a_done));
+                            mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
+                            mbar_wait(ctx, &M.o_free, (n_ofree++ & 1u) ^ 1u);
+                            tc_fence_after();
+#pragma unroll
+                            for (uint32_t ks = 0; ks < 4; ++ks)
+                                umma_f16(tmO, umma_desc_sw128(tq + ks * 32u),
+                                         umma_desc_sw128(base + kOffS16 + ks * 2048u, 8192), idO1, ks);
+                            mbar_wait(ctx, &M.a16_ready, n_a16++ & 1u);
+                            tc_fence_after();
+#pragma unroll
+                            for (uint32_t ks = 0; ks < 4; ++ks)
+                                umma_f16(tmO, umma_desc_sw128(ta16 + ks * 32u),
+                                         umma_desc_sw128(tv + ks * 2048u, 8192), idO1, 1);
+                            umma_commit(smem_u32(&M.o_done));
+                        }
+#pragma unroll
+                        for (uint32_t ks = 0; ks < 4; ++ks)
+                            umma_f16(tmS, umma_desc_sw128(tk + ks * 2048u, 8192),
+                                     umma_desc_sw128(tv + ks * 2048u, 8192), idS, ks);
+                        umma_commit(smem_u32(&M.s_done));
+                    }
+                }
+            }
+            __syncwarp();
+        } else {
+            // ------------------------------------------------------------ compute warps
+            const size_t srow = (static_cast<size_t>(it.seq) * kD + my_c) * kD;   // row of a [B,H,K,V] state
+            const size_t slot = static_cast<size_t>(it.seq) * P.NS + it.seg;
+            uint32_t ctr = chunk_ctr;
+            float gsum = 0.f;       // log of the segment's total decay for channel my_c
+
+            auto load_initial = [&]() {
+#pragma unroll
+                for (int x = 0; x < kD; ++x) S[x] = 0.f;
+                if (owner && P.s0 != nullptr) {
+                    const float4* src = reinterpret_cast<const float4*>(P.s0 + srow);
+#pragma unroll
+                    for (int x = 0; x < kD / 4; ++x) {
+                        const float4 v4 = __ldg(src + x);
+                        S[4 * x] = v4.x; S[4 * x + 1] = v4.y; S[4 * x + 2] = v4.z; S[4 * x + 3] = v4.w;
+                    }
+                }
+            };
+
+            if (it.state_pass) {
+                // ---------------- pass 1: reduce the segment to (decay, increment)
+                if (it.seg == 0) load_initial();
+                else {
+#pragma unroll
+                    for (int x = 0; x < kD; ++x) S[x] = 0.f;
+                }
+                {
+                    const uint32_t s = ctr % kNumStages;
+                    mbar_wait(ctx, &M.full[s], n_full[s]++ & 1u);
+                    gate_math<true>(ctx, base + kOffStage + s * kStageBytes, ctr,
+                                    chunk_valid(it.first_chunk * kChunk, P.T), w, l);
+                    mbar_arrive(smem_u32(&M.ops_ready));
+                }
+                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                    const uint32_t s = ctr % kNumStages;
+                    if (i + 1 < it.nchunks) {
+                        const uint32_t s1 = (ctr + 1) % kNumStages;
+                        mbar_wait(ctx, &M.full[s1], n_full[s1]++ & 1u);
+                        gate_math<true>(ctx, base + kOffStage + s1 * kStageBytes, ctr + 1,
+                                        chunk_valid((it.first_chunk + i + 1) * kChunk, P.T), w, l);
+                    }
+                    mbar_wait(ctx, &M.s_done, n_sdone++ & 1u);
+                    tc_fence_after();
+                    float x[kD];
+                    tmem_row64(tmem, w, 128, x);
+                    const float b4 = M.b4s[ctr & 1][my_c];
+                    const float dec = fast_exp(b4);
+                    gsum += b4;
+#pragma unroll
+                    for (int v = 0; v < kD; ++v) S[v] = fmaf(dec, S[v], x[v]);
+                    tc_fence_before();
+                    if (tid == 0) mbar_arrive(smem_u32(&M.empty[s]));
+                    if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.ops_ready));
+                }
+                // ---------------- publish, look back, publish the inclusive state
+                float* my_agg = P.agg + slot * kAggStride;
+                float* my_incl = P.incl + slot * (kD * kD);
+                if (it.seg == 0) {
+                    if (owner) {
+                        float4* dst = reinterpret_cast<float4*>(my_incl + my_c * kD);
+#pragma unroll
+                        for (int x4 = 0; x4 < kD / 4; ++x4)
+                            dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
+                    }
+                    __threadfence();
+                    named_bar_sync(1, kComputeThreads);
+                    if (tid == 0) st_release_gpu(P.flags + slot, 2u);
+                    load_initial();
+                } else {
+                    if (owner) {
+                        float4* dst = reinterpret_cast<float4*>(my_agg + my_c * kD);
+#pragma unroll
+                        for (int x4 = 0; x4 < kD / 4; ++x4)
+                            dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
+                        my_agg[kD * kD + my_c] = gsum;
+                    }
+                    __threadfence();
+                    named_bar_sync(1, kComputeThreads);
+                    if (tid == 0) st_release_gpu(P.flags + slot, 1u);
+                }
+            } else if (it.seg == 0) {
+                load_initial();
+            }
+            if (it.seg > 0) {
+                // decoupled look-back: S <- state entering this segment
+#pragma unroll
+                for (int x = 0; x < kD; ++x) S[x] = 0.f;
+                float dlog = 0.f;
+                int j = it.seg - 1;
+                const uint64_t t0 = globaltimer_ns();
+                while (true) {
+                    const size_t sj = static_cast<size_t>(it.seq) * P.NS + j;
+                    uint32_t f = ld_acquire_gpu(P.flags + sj);
+                    while (f == 0u) {
+                        if (M.abort || ld_acquire_gpu(P.ctrl + 1) != 0u) break;
+                        if (globaltimer_ns() - t0 > ctx.deadline_span_ns) {
+                            raise_timeout(ctx, WHERE_LOOKBACK);
+                            break;
+                        }
+                        __nanosleep(64);
+                        f = ld_acquire_gpu(P.flags + sj);
+                    }
+                    // one decision per warp: the inclusive state only if every lane has seen it published
+                    const bool gave_up = __any_sync(0xffffffffu, f == 0u);
+                    const bool inclusive = __all_sync(0xffffffffu, f == 2u);
+                    if (gave_up) break;   // result undefined, status word set
+                    const float dacc = fast_exp(dlog);
+                    if (inclusive) {
+                        if (owner) {
+                            const float4* src = reinterpret_cast<const float4*>(P.incl + sj * (kD * kD) + my_c * kD);
+#pragma unroll
+                            for (int x4 = 0; x4 < kD / 4; ++x4) {
+                                const float4 v4 = __ldcg(src + x4);
+                                S[4 * x4] = fmaf(dacc, v4.x, S[4 * x4]);
+                                S[4 * x4 + 1] = fmaf(dacc, v4.y, S[4 * x4 + 1]);
+                                S[4 * x4 + 2] = fmaf(dacc, v4.z, S[4 * x4 + 2]);
+                                S[4 * x4 + 3] = fmaf(dacc, v4.w, S[4 * x4 + 3]);
+                            }
+                        }
+                        break;
+                    }
+                    if (owner) {
+                        const float* aj = P.agg + sj * kAggStride;
+                        const float4* src = reinterpret_cast<const float4*>(aj + my_c * kD);
+#pragma unroll
+                        for (int x4 = 0; x4 < kD / 4; ++x4) {
+                            const float4 v4 = __ldcg(src + x4);
+                            S[4 * x4] = fmaf(dacc, v4.x, S[4 * x4]);
+                            S[4 * x4 + 1] = fmaf(dacc, v4.y, S[4 * x4 + 1]);
+                            S[4 * x4 + 2] = fmaf(dacc, v4.z, S[4 * x4 + 2]);
+                            S[4 * x4 + 3] = fmaf(dacc, v4.w, S[4 * x4 + 3]);
+                        }
+                        dlog += __ldcg(aj + kD * kD + my_c);
+                    }
+                    --j;   // j >= 0 always holds here: segment 0 only ever publishes an inclusive state
+                    if (j < 0) break;
+                }
+                if (it.state_pass) {
+                    // inclusive state after this segment = decay * incoming + increment
+                    if (owner) {
+                        const float dseg = fast_exp(gsum);
+                        const float4* inc = reinterpret_cast<const float4*>(P.agg + slot * kAggStride + my_c * kD);
+                        float4* dst = reinterpret_cast<float4*>(P.incl + slot * (kD * kD) + my_c * kD);
+#pragma unroll
+                        for (int x4 = 0; x4 < kD / 4; ++x4) {
+                            const float4 a4 = __ldcg(inc + x4);
+                            dst[x4] = make_float4(fmaf(dseg, S[4 * x4], a4.x), fmaf(dseg, S[4 * x4 + 1], a4.y),
+                                                  fmaf(dseg, S[4 * x4 + 2], a4.z), fmaf(dseg, S[4 * x4 + 3], a4.w));
+                        }
+                    }
+                    __threadfence();
+                    named_bar_sync(1, kComputeThreads);
+                    if (tid == 0) st_release_gpu(P.flags + slot, 2u);
+                }
+            }
+
+            // ---------------- pass 2: outputs
+            if (owner) store_row_f16(base + kOffS16, my_c, S);
+            fence_proxy_async_smem();
+            mbar_arrive(smem_u32(&M.s16_ready));
+            {
+                const uint32_t s = ctr % kNumStages;
+                mbar_wait(ctx, &M.full[s], n_full[s]++ & 1u);
+                gate_math<false>(ctx, base + kOffStage + s * kStageBytes, ctr,
+                                 chunk_valid(it.first_chunk * kChunk, P.T), w, l);
+                mbar_arrive(smem_u32(&M.ops_ready));
+            }
+            for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                const uint32_t s = ctr % kNumStages;
+                const uint32_t stage = base + kOffStage + s * kStageBytes;
+                const uint32_t rho = 16 * w + (l & 15);
+                float x[kD];
+                // scores: TMEM -> causal mask -> fp16 tile (takes the place of the raw gate tile)
+                mbar_wait(ctx, &M.a_done, n_adone++ & 1u);
+                tc_fence_after();
+                if (!M.wide[ctr & 1]) {
+                    tmem_row64(tmem, w, 0, x);
+                    if (owner) {
+#pragma unroll
+                        for (uint32_t j = 0; j < kD; ++j) {
+                            const bool keep = P.rev ? (j >= rho) : (j <= rho);
+                            x[j] = keep ? x[j] : 0.f;
+                        }
+                        store_row_f16(stage + 2 * kTileBytes, rho, x);
+                    }
+                } else {
+                    named_bar_sync(1, kComputeThreads);
+                    exact_scores(ctx, stage + 2 * kTileBytes, tid);
+                }
+                fence_proxy_async_smem();
+                tc_fence_before();
+                mbar_arrive(smem_u32(&M.a16_ready));
+                // gate math of the next chunk overlaps the A.V and state MMAs of this one
+                if (i + 1 < it.nchunks) {
+                    const uint32_t s1 = (ctr + 1) % kNumStages;
+                    mbar_wait(ctx, &M.full[s1], n_full[s1]++ & 1u);
+                    gate_math<false>(ctx, base + kOffStage + s1 * kStageBytes, ctr + 1,
+                                     chunk_valid((it.first_chunk + i + 1) * kChunk, P.T), w, l);
+                    mbar_arrive(smem_u32(&M.ops_ready));
+                }
+                // outputs: TMEM -> scale -> fp16 tile (takes the place of qh) -> TMA store
+                mbar_wait(ctx, &M.o_done, n_odone++ & 1u);
+                tc_fence_after();
+                tmem_row64(tmem, w, 64, x);
+                tc_fence_before();
+                mbar_arrive(smem_u32(&M.o_free));
+                if (owner) {
+#pragma unroll
+                    for (int v = 0; v < kD; ++v) x[v] *= P.scale;
+                    store_row_f16(stage, rho, x);
+                }
+                fence_proxy_async_smem();
+                named_bar_sync(1, kComputeThreads);
+                if (tid == 0) {
+                    const int p0 = (it.first_chunk + i) * kChunk;
+                    for_each_box(p0, P.T, P.Hc, P.rev, [&](int id, int r, int c, int row) {
+                        tma_store_5d(&maps.m[TO][id], stage + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
+                    });
+                    tma_store_commit();
+                }
+                // state: S <- exp(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
+                mbar_wait(ctx, &M.s_done, n_sdone++ & 1u);
+                tc_fence_after();
+                tmem_row64(tmem, w, 128, x);
+                tc_fence_before();
+                {
+                    const float dec = fast_exp(M.b4s[ctr & 1][my_c]);
+#pragma unroll
+                    for (int v = 0; v < kD; ++v) S[v] = fmaf(dec, S[v], x[v]);
+                }
+                if (i + 1 < it.nchunks) {
+                    if (owner) store_row_f16(base + kOffS16, my_c, S);
+                    fence_proxy_async_smem();
+                    mbar_arrive(smem_u32(&M.s16_ready));
+                }
+                if (tid == 0) {
+                    tma_store_wait_read();
+                    mbar_arrive(smem_u32(&M.empty[s]));
+                }
+            }
+            if (it.seg == P.NS - 1 && P.sT != nullptr && owner) {
+                float4* dst = reinterpret_cast<float4*>(P.sT + srow);
+#pragma unroll
+                for (int x4 = 0; x4 < kD / 4; ++x4)
+                    dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
+            }
+        }
+        chunk_ctr += static_cast<uint32_t>(npass * it.nchunks);
+        __syncthreads();   // the item is drained: every role restarts from the same counters
+    }
+
+    if (tid == 0) tma_store_wait_all();
+    tc_fence_before();
+    __syncthreads();
+    if (w == 4) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace gla

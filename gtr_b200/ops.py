@@ -1,0 +1,184 @@
+"""Python face of the B200 GLA forward operator.
+
+Two call styles are kept so the operator drops in where the reference calls its own:
+
+* the extension style of the reference's ``gla_torch_ext`` module
+  (engine/gtr/backbone/csrc/gla_torch_ext.cu:263-293): ``chunk_gla_run``,
+  ``chunk_gla_run_gated``, ``chunk_gla_with_ws``, ``workspace_floats``, ``make_workspace``,
+  ``rmsnorm_gated`` and the constants ``kK``, ``kV``, ``kBT`` -- caller-owned workspace and
+  output, nothing allocated, returns None;
+* the FLA style the backbone falls back to (engine/gtr/backbone/vit_adapter.py:566-568):
+  ``chunk_gla(q, k, v, g, scale=None, initial_state=None, output_final_state=False)``
+  returning ``(o, final_state)``.
+
+Both take two extra keywords the reference expresses by physically permuting tokens between
+blocks (engine/gtr/backbone/vit_adapter_spatial_swiglu.py:88-94): ``direction`` (0 row, 1 row
+reversed, 2 column, 3 column reversed; or the names) and ``grid_hw``.  Inputs and outputs
+always stay in canonical token order.
+
+Everything here runs through libgla_b200.so; there is no PyTorch or CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+kK = 64
+kV = 64
+kBT = 64
+
+DIRECTIONS = ("row", "row_rev", "col", "col_rev")
+
+
+def _direction_id(direction) -> int:
+    if isinstance(direction, str):
+        if direction not in DIRECTIONS:
+            raise ValueError(f"direction must be one of {DIRECTIONS} or 0..3, got {direction!r}")
+        return DIRECTIONS.index(direction)
+    return int(direction)
+
+
+def _check_tensor(x: torch.Tensor, name: str, last: int, like: Optional[torch.Tensor] = None) -> None:
+    if not isinstance(x, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not x.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if x.dtype != torch.float16:
+        raise RuntimeError(f"{name} must be float16, got {x.dtype}")
+    if x.dim() != 4:
+        raise RuntimeError(f"{name} must be [B, T, H, D], got {tuple(x.shape)}")
+    if x.shape[-1] != last:
+        raise RuntimeError(f"{name}: last dim must be {last}, got {x.shape[-1]}")
+    if x.numel() and x.stride(-1) != 1:
+        raise RuntimeError(f"{name}: innermost dimension must be dense")
+    if like is not None and (x.shape[:3] != like.shape[:3] or x.device != like.device):
+        raise RuntimeError(f"{name}: shape/device {tuple(x.shape)}/{x.device} does not match q "
+                           f"{tuple(like.shape)}/{like.device}")
+
+
+def _strides(x: torch.Tensor):
+    return (ctypes.c_int64 * 3)(x.stride(0), x.stride(1), x.stride(2))
+
+
+def workspace_bytes(B: int, T: int, H: int) -> int:
+    """Bytes of scratch one forward of this shape needs (reference: workspace_floats)."""
+    return int(_lib.lib().gla_b200_workspace_bytes(B, T, H, kK, kV))
+
+
+def workspace_floats(B: int, T: int, H: int) -> int:
+    return (workspace_bytes(B, T, H) + 3) // 4
+
+
+def make_workspace(B: int, T: int, H: int, device) -> torch.Tensor:
+    """fp32 scratch tensor for (B, T, H); reusable across calls of that shape or smaller."""
+    return torch.zeros(max(workspace_floats(B, T, H), 64), dtype=torch.float32, device=device)
+
+
+def _forward(q, k, v, gk, o, ws, scale, gk_normalizer, direction, grid_hw, initial_state, final_state,
+             out_gate=None, rms_w=None, eps=0.0, segments=0, wait_limit=0) -> None:
+    _check_tensor(q, "q", kK)
+    _check_tensor(k, "k", kK, q)
+    _check_tensor(gk, "gk", kK, q)
+    _check_tensor(v, "v", kV, q)
+    _check_tensor(o, "o", kV, q)
+    B, T, H, _ = q.shape
+    a = _lib.Args()
+    a.q, a.k, a.v, a.g, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), gk.data_ptr(), o.data_ptr()
+    a.q_stride, a.k_stride, a.v_stride = _strides(q), _strides(k), _strides(v)
+    a.g_stride, a.o_stride = _strides(gk), _strides(o)
+    if out_gate is not None or rms_w is not None:
+        if out_gate is None or rms_w is None:
+            raise RuntimeError("the fused epilogue needs both the output gate and the RMSNorm weight")
+        _check_tensor(out_gate, "g", kV, q)
+        if rms_w.dtype != torch.float16 or rms_w.numel() != kV or not rms_w.is_contiguous() or rms_w.device != q.device:
+            raise RuntimeError("rms_w must be a contiguous float16 vector of 64 elements on q's device")
+        a.out_gate, a.rms_weight, a.rms_eps = out_gate.data_ptr(), rms_w.data_ptr(), float(eps)
+        a.gate_stride = _strides(out_gate)
+    for name, s in (("initial_state", initial_state), ("final_state", final_state)):
+        if s is None:
+            continue
+        if (s.dtype != torch.float32 or tuple(s.shape) != (B, H, kK, kV) or not s.is_contiguous()
+                or s.device != q.device):
+            raise RuntimeError(f"{name} must be a contiguous float32 [B, H, {kK}, {kV}] tensor on q's device")
+    a.initial_state = initial_state.data_ptr() if initial_state is not None else None
+    a.final_state = final_state.data_ptr() if final_state is not None else None
+    if not isinstance(ws, torch.Tensor) or not ws.is_cuda or ws.device != q.device or not ws.is_contiguous():
+        raise RuntimeError("ws must be a contiguous CUDA tensor on q's device (see make_workspace)")
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
+    a.B, a.T, a.H, a.K, a.V = B, T, H, kK, kV
+    if grid_hw is not None:
+        a.grid_h, a.grid_w = int(grid_hw[0]), int(grid_hw[1])
+    a.direction = _direction_id(direction)
+    a.segments = int(segments)
+    a.scale = float(scale)
+    a.gk_normalizer = float(gk_normalizer)
+    a.wait_limit = int(wait_limit)
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        _lib.check(_lib.lib().gla_b200_forward(ctypes.byref(a), ctypes.c_void_p(stream)))
+
+
+def chunk_gla_run(q, k, v, gk, scale, ws, o, gk_normalizer: float = 0.0, *, direction=0, grid_hw=None,
+                  initial_state=None, final_state=None, segments: int = 0, wait_limit: int = 0) -> None:
+    """o <- GLA(q, k, v, gk) on the current stream.  Reference: ext.chunk_gla_run (gla_torch_ext.cu:40-90)."""
+    _forward(q, k, v, gk, o, ws, scale, gk_normalizer, direction, grid_hw, initial_state, final_state,
+             segments=segments, wait_limit=wait_limit)
+
+
+def chunk_gla_run_gated(q, k, v, gk, g, rms_w, scale, eps, ws, y, gk_normalizer: float = 0.0, *, direction=0,
+                        grid_hw=None, initial_state=None, final_state=None, segments: int = 0) -> None:
+    """y <- RMSNorm(GLA(q,k,v,gk)) * rms_w * silu(g).  Reference: ext.chunk_gla_run_gated (gla_torch_ext.cu:92-154)."""
+    _forward(q, k, v, gk, y, ws, scale, gk_normalizer, direction, grid_hw, initial_state, final_state,
+             out_gate=g, rms_w=rms_w, eps=eps, segments=segments)
+
+
+def chunk_gla_with_ws(q, k, v, gk, scale, ws, **kw) -> torch.Tensor:
+    """Allocates the output only.  Reference: ext.chunk_gla_with_ws (gla_torch_ext.cu:222-226)."""
+    o = torch.empty(*q.shape[:3], kV, dtype=torch.float16, device=q.device)
+    chunk_gla_run(q, k, v, gk, scale, ws, o, **kw)
+    return o
+
+
+def chunk_gla(q, k, v, g, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,
+              output_final_state: bool = False, cu_seqlens=None, *, direction=0, grid_hw=None,
+              gk_normalizer: float = 0.0, segments: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """FLA-style call: returns (o, final_state).  Allocates output, workspace and final state."""
+    if cu_seqlens is not None:
+        raise NotImplementedError("variable-length batches (cu_seqlens) are not part of this operator")
+    B, T, H, K = q.shape
+    if scale is None:
+        scale = K ** -0.5
+    ws = make_workspace(B, T, H, q.device)
+    o = torch.empty(B, T, H, kV, dtype=torch.float16, device=q.device)
+    final = torch.empty(B, H, kK, kV, dtype=torch.float32, device=q.device) if output_final_state else None
+    chunk_gla_run(q, k, v, g, scale, ws, o, gk_normalizer, direction=direction, grid_hw=grid_hw,
+                  initial_state=initial_state, final_state=final, segments=segments)
+    return o, final
+
+
+def check_status(ws: torch.Tensor) -> None:
+    """Synchronise the current stream and raise if a bounded wait expired inside the last forward using `ws`."""
+    with torch.cuda.device(ws.device):
+        stream = torch.cuda.current_stream(ws.device).cuda_stream
+        _lib.check(_lib.lib().gla_b200_check_status(ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(stream)))
+
+
+def rmsnorm_gated(x, g, w, y, eps: float) -> None:
+    """y <- x * rsqrt(mean(x^2) + eps) * w * silu(g), rows of 64.  Reference: ext.rmsnorm_gated
+    (gla_torch_ext.cu:228-261; kernel gla_norm_gate.cuh:13-75).  y may alias x."""
+    for t, name in ((x, "x"), (g, "g"), (y, "y")):
+        if not t.is_cuda or t.dtype != torch.float16 or not t.is_contiguous() or t.shape[-1] != kV:
+            raise RuntimeError(f"{name} must be a contiguous float16 CUDA tensor with last dim {kV}")
+    if g.shape != x.shape or y.shape != x.shape:
+        raise RuntimeError("x, g and y must have the same shape")
+    if w.dtype != torch.float16 or w.numel() != kV or not w.is_contiguous() or w.device != x.device:
+        raise RuntimeError("w must be a contiguous float16 vector of 64 elements on x's device")
+    rows = x.numel() // kV
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        _lib.check(_lib.lib().gla_b200_rmsnorm_gated(x.data_ptr(), g.data_ptr(), w.data_ptr(), y.data_ptr(),
+                                                     rows, kV, float(eps), ctypes.c_void_p(stream)))

@@ -1,0 +1,118 @@
+/*
+ * gla_b200 -- C ABI of the B200 (sm_100a) chunkwise gated-linear-attention forward operator.
+ *
+ * Plain pointers and sizes only: this is the boundary a host in any language binds to
+ * (ctypes, pybind, a TensorRT plugin's enqueue).  Each entry point names the interface of
+ * the GTR reference it stands in for (paths relative to the GTR project root).
+ *
+ * Tensor contract (reference: engine/gtr/backbone/csrc/gla_torch_ext.cu:15-22,49-66):
+ *   q, k, g : fp16 [B, T, H, K]      v, o, out_gate : fp16 [B, T, H, V]      K = V = 64
+ *   g is the log-space forget gate (<= 0), or raw logits when gk_normalizer > 0, in which
+ *   case the kernel applies logsigmoid(g) / gk_normalizer (gla_chunk.cuh:775,788-790).
+ *   States are fp32 [B, H, K, V].  All pointers are device pointers, 16-byte aligned.
+ *   Unlike the reference, tensors need not be contiguous: each has element strides for
+ *   (batch, token, head); the innermost dimension must be dense.  A stride triple of
+ *   {0,0,0} means contiguous.  Strides must be multiples of 8 elements (16 bytes).
+ *
+ * Recurrence computed, per batch b and head h, along the scan order p = 0..T-1:
+ *   S_p = exp(g_p)[:,None] * S_{p-1} + k_p v_p^T ,   o_p = scale * q_p^T S_p
+ * `direction` selects which token each step p reads on the grid_h x grid_w patch grid
+ * (reference: engine/gtr/backbone/vit_adapter_spatial_swiglu.py:88-94, the physical token
+ * permutation applied between backbone blocks; here it is folded into the tile coordinates):
+ *   0 row-major, 1 row-major reversed, 2 column-major, 3 column-major reversed.
+ *   Outputs are written at the token's own (unpermuted) position.
+ */
+#ifndef GLA_B200_H_
+#define GLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GLA_B200_VERSION 1
+#define GLA_B200_CHUNK 64          /* tokens per chunk; reference kBT, gla_chunk.cuh:16 */
+#define GLA_B200_HEAD_K 64         /* reference kK is 32 (gla_chunk.cuh:14); this build serves K = 64 */
+#define GLA_B200_HEAD_V 64         /* reference kV, gla_chunk.cuh:15 */
+
+enum gla_b200_direction {
+    GLA_B200_ROW = 0, GLA_B200_ROW_REV = 1, GLA_B200_COL = 2, GLA_B200_COL_REV = 3
+};
+
+enum gla_b200_error {
+    GLA_B200_OK = 0,
+    GLA_B200_ERR_NULL = -1,          /* a required pointer is NULL */
+    GLA_B200_ERR_SHAPE = -2,         /* unsupported B/T/H/K/V or grid_h*grid_w != T */
+    GLA_B200_ERR_ALIGN = -3,         /* pointer or stride not 16-byte aligned */
+    GLA_B200_ERR_DIRECTION = -4,     /* direction outside 0..3 */
+    GLA_B200_ERR_WORKSPACE = -5,     /* workspace missing or smaller than gla_b200_workspace_bytes */
+    GLA_B200_ERR_DEVICE = -6,        /* not an sm_100 device, or driver entry point unavailable */
+    GLA_B200_ERR_CUDA = -7,          /* a CUDA runtime/driver call failed (see gla_b200_last_cuda_error) */
+    GLA_B200_ERR_TIMEOUT = -8,       /* device status word: a bounded wait inside the kernel expired */
+    GLA_B200_ERR_ARG = -9            /* any other invalid argument */
+};
+
+typedef struct gla_b200_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    const void* g;
+    void* o;
+    /* optional: fused RMSNorm * weight * silu(out_gate) epilogue (reference chunk_gla_run_gated,
+     * gla_torch_ext.cu:92-154); both NULL for the plain operator */
+    const void* out_gate;
+    const void* rms_weight;          /* fp16 [V] */
+    /* optional fp32 [B,H,K,V] states (FLA call signature, vit_adapter.py:566-568) */
+    const float* initial_state;
+    float* final_state;
+    /* caller-owned scratch, >= gla_b200_workspace_bytes(B,T,H,K,V), 256-byte aligned */
+    void* workspace;
+    size_t workspace_bytes;
+    int64_t q_stride[3], k_stride[3], v_stride[3], g_stride[3], o_stride[3], gate_stride[3];
+    int32_t B, T, H, K, V;
+    int32_t grid_h, grid_w;          /* patch grid; needed for directions 2,3; 0,0 means 1 x T */
+    int32_t direction;
+    int32_t segments;                /* chunks of one sequence handled per work item; 0 = automatic */
+    float scale;                     /* applied to the output, reference default K^-0.5 */
+    float gk_normalizer;             /* 0: g is a log gate; >0: g holds logits */
+    float rms_eps;
+    uint32_t wait_limit;             /* polls before a device-side wait gives up; 0 = default */
+} gla_b200_args;
+
+/* Replaces chunk_gla_run / chunk_gla_run_gated (gla_torch_ext.cu:40-154) and
+ * gla_chunk::launch_chunk_gla (gla_chunk.cuh:1446-1540).  Enqueues on `stream`
+ * (a cudaStream_t), never synchronises, never allocates; capturable in a CUDA graph once
+ * the calling thread has run the same shape once.  Returns 0 or a gla_b200_error. */
+int gla_b200_forward(const gla_b200_args* args, void* stream);
+
+/* Replaces workspace_floats (gla_torch_ext.cu:24-33); bytes, not floats.  0 on bad shape. */
+size_t gla_b200_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_t K, int32_t V);
+
+/* Reads the device status word of a workspace after synchronising `stream`:
+ * 0, or GLA_B200_ERR_TIMEOUT when a bounded wait expired during the last forward.
+ * The reference has no counterpart (its waits are unbounded, gla_chunk.cuh:1229-1233). */
+int gla_b200_check_status(const void* workspace, void* stream);
+
+/* Replaces rmsnorm_gated (gla_torch_ext.cu:156-196, kernel gla_norm_gate.cuh:13-75):
+ * y = x * rsqrt(mean(x^2) + eps) * w * silu(g) over rows of D = 64 fp16 values; y may alias x. */
+int gla_b200_rmsnorm_gated(const void* x, const void* g, const void* w, void* y,
+                           int64_t rows, int32_t D, float eps, void* stream);
+
+/* Shape of GLAPlugin::enqueue (tensorrt_plugin/trt_plugin/gla_plugin.cu:124-163): `inputs` holds
+ * q,k,v,gk[,g,rms_w] device pointers, `outputs[0]` the result, dims are those of q [B,T,H,K];
+ * the fused epilogue is used iff n_inputs == 6 and rms_eps > 0 (gla_plugin.cu:150).
+ * Returns 0 or -1 like the plugin. */
+int32_t gla_b200_trt_enqueue(const void* const* inputs, int32_t n_inputs, void* const* outputs,
+                             const int64_t* q_dims, float scale, float gk_normalizer, float rms_eps,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+const char* gla_b200_strerror(int code);
+const char* gla_b200_last_cuda_error(void);
+int gla_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLA_B200_H_ */
