@@ -158,12 +158,15 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 }
 
 // ------------------------------------------------------------------ small numeric helpers
-__device__ __forceinline__ float fast_exp(float x) { return exp2f(x * 1.4426950408889634f); }
-
-__device__ __forceinline__ float to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+__device__ __forceinline__ float ex2(float x) {   // 2^x, one MUFU op; results below 2^-126 flush to zero
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Round to the 10-bit tf32 mantissa (nearest, ties away) with two integer ops; kind::tf32 reads
+// only the upper 19 bits of each operand, so unrounded values would be truncated.
+__device__ __forceinline__ float round_tf32(float x) {
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
 // two floats -> packed fp16 pair, round to nearest, saturating to the largest finite value
 __device__ __forceinline__ uint32_t pack_half2_sat(float lo, float hi) {

@@ -10,14 +10,21 @@
 // produce the outputs.  Replaces chunk_compute_S_kernel / chunk_scan_*_kernel /
 // chunk_fwd_o_kernel of the reference (engine/gtr/backbone/csrc/gla_chunk.cuh:718-1394).
 //
-// Per chunk, with G the inclusive within-chunk cumulative log gate (fp32), G_m its value at
-// the middle row and G_L at the last row:
-//   qh = q*exp(G)      kh = k*exp(G_L-G)       (fp16, exponents <= 0)
-//   qb = qh*exp(-G_m)  kb = kh*exp(G_m-G_L)    (tf32: fp32 range, exponents within +-64)
+// Per chunk, with G the inclusive within-chunk cumulative log gate (fp32, kept in log2
+// units), G_m its value at the middle row and G_L at the last row:
+//   qh = q*2^G        kh = k*2^(G_L-G)         (fp16, exponents <= 0)
+//   qb = qh*2^(-G_m)  kb = kh*2^(G_m-G_L)      (tf32: fp32 range, exponents within +-92)
 //   A  = tril(qb kb^T)                 tcgen05.mma kind::tf32  -> TMEM
 //   O  = qh S_in + A v                 two tcgen05.mma kind::f16 into one TMEM accumulator
-//   S' = exp(G_L) (.) S_in + kh^T v    tcgen05.mma kind::f16, decay applied in registers (fp32)
-// A chunk whose total decay exceeds e^-64 in any channel takes an exact scalar path for A.
+//   S' = 2^(G_L) (.) S_in + kh^T v     tcgen05.mma kind::f16, decay applied in registers (fp32)
+// A chunk whose total decay exceeds 2^-92 (e^-64) in any channel takes an exact scalar path for A.
+//
+// Tensor memory.  An M = 64 accumulator occupies lanes 0-15 of each 32-lane quadrant, so two
+// accumulators share the same columns at lane offsets 0 and 16.  A is produced as two N = 32
+// halves (key rows 0-31 at lane offset 0, 32-63 at offset 16); O sits at offset 0 and the
+// state increment at offset 16 of the same columns.  Every lane of the four compute warps
+// therefore owns useful data: lanes 0-15 of warp w hold row 16w+l of O (and the left half of
+// A), lanes 16-31 hold state row 16w+l-16 (and the right half of A).
 //
 // Warp roles: warps 0-3 gate math, TMEM epilogues, state; warp 4 TMA producer; warp 5 MMA issue.
 #pragma once
@@ -33,8 +40,12 @@ constexpr int kStageBytes = 4 * kTileBytes;
 constexpr int kNumStages = 2;
 constexpr int kComputeThreads = 128;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 256;
-constexpr float kWideLimit = 64.f;        // largest total in-chunk decay (nats) the tf32 path takes
+constexpr int kTmemCols = 128;
+constexpr uint32_t kTmA = 0;              // scores: 32 columns, two interleaved halves
+constexpr uint32_t kTmOS = 32;            // outputs (lane offset 0) and state increment (lane offset 16)
+constexpr uint32_t kLane16 = 16u << 16;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kWideLimit = 64.f * kLog2e;   // largest in-chunk decay (log2 units) the tf32 path takes
 
 // tensor ids inside Maps
 enum { TQ = 0, TK = 1, TG = 2, TV = 3, TO = 4, TGATE = 5, kNumTensors = 6 };
@@ -59,7 +70,7 @@ struct Params {
     float* sT;
     uint32_t* ctrl;      // [0] ticket, [1] status
     uint32_t* flags;     // per (sequence, segment): 0 none, 1 aggregate, 2 inclusive state
-    float* agg;          // per (sequence, segment): 4096 state increment + 64 log decay
+    float* agg;          // per (sequence, segment): 4096 state increment + 64 log2 decay
     float* incl;         // per (sequence, segment): 4096 state after the segment
     uint32_t wait_limit_us;
 };
@@ -78,13 +89,13 @@ constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + alignment slack
 struct Misc {
     uint64_t full[kNumStages];
     uint64_t empty[kNumStages];
-    uint64_t ops_ready, a_done, a16_ready, o_done, o_free, s_done, s16_ready;
+    uint64_t ops_ready, a_done, a16_ready, os_done, acc_free, s16_ready;
     uint32_t tmem_base;
     volatile uint32_t abort;
     int item;
     uint32_t wide[2];
-    float tot[2][4][kD];
-    float b4s[2][kD];
+    alignas(16) float tot[2][4][kD];   // per-warp gate sums of the two chunks in flight (read as float2)
+    alignas(16) float b4s[2][kD];      // chunk totals G_L per channel
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "misc block too large");
 
@@ -93,7 +104,8 @@ enum { WHERE_MBAR = 1, WHERE_LOOKBACK = 2 };
 struct Ctx {
     const Params* p;
     Misc* misc;
-    uint32_t smem;       // shared address of the 1024-aligned base
+    uint8_t* base;       // generic pointer to the 1024-aligned shared-memory base
+    uint32_t smem;       // the same as a shared-window address
     uint64_t deadline_span_ns;
 };
 
@@ -105,36 +117,32 @@ __device__ __forceinline__ void raise_timeout(const Ctx& c, uint32_t where) {
 // Bounded wait.  After a time-out in this CTA every later wait returns at once, so all warps
 // keep following the protocol (arrivals, named barriers) and the CTA drains and exits; the
 // result is then undefined and the status word says so.
-__device__ __forceinline__ void mbar_wait(const Ctx& c, uint64_t* bar, uint32_t parity) {
-    const uint32_t b = smem_u32(bar);
-    if (mbar_try_wait(b, parity)) return;
+__device__ __noinline__ void mbar_wait_slow(const Ctx& c, uint32_t b, uint32_t parity) {
     const uint64_t t0 = globaltimer_ns();
+    uint32_t n = 0;
     while (true) {
-        if (c.misc->abort) return;
         if (mbar_try_wait(b, parity)) return;
-        if (globaltimer_ns() - t0 > c.deadline_span_ns) {
-            raise_timeout(c, WHERE_MBAR);
-            return;
+        if ((++n & 63u) == 0u) {
+            if (c.misc->abort) return;
+            if (globaltimer_ns() - t0 > c.deadline_span_ns) {
+                raise_timeout(c, WHERE_MBAR);
+                return;
+            }
         }
     }
 }
-
-// ---- addressing inside 128-byte-swizzled tiles -------------------------------------------
-__device__ __forceinline__ uint32_t sw_f16(uint32_t row, uint32_t col) {     // col in fp16 elements
-    return row * 128u + ((((col >> 3) ^ row) & 7u) << 4) + ((col & 7u) << 1);
-}
-__device__ __forceinline__ uint32_t sw_f32(uint32_t row, uint32_t col) {     // col in fp32 elements, 0..63
-    const uint32_t c = col & 31u;
-    return (col >> 5) * kTileBytes + row * 128u + ((((c >> 2) ^ row) & 7u) << 4) + ((c & 3u) << 2);
+__device__ __forceinline__ void mbar_wait(const Ctx& c, uint64_t* bar, uint32_t parity) {
+    const uint32_t b = smem_u32(bar);
+    if (mbar_try_wait(b, parity)) return;
+    mbar_wait_slow(c, b, parity);
 }
 
 // Enumerate the TMA boxes that cover chunk [p0, p0+64) of the scan.  f(box_id, r, c, smem_row).
 template <class F>
-__device__ __forceinline__ int for_each_box(int p0, int L, int Hc, int rev, F f) {
+__device__ __forceinline__ void for_each_box(int p0, int L, int Hc, int rev, F f) {
     const int u_lo = rev ? (L - p0 - kChunk) : p0;
     int u0 = max(u_lo, 0);
     const int u1 = min(u_lo + kChunk, L);
-    const int valid = u1 - u0;
     while (u0 < u1) {
         const int c = u0 / Hc;
         int r = u0 - c * Hc;
@@ -148,162 +156,176 @@ __device__ __forceinline__ int for_each_box(int p0, int L, int Hc, int rev, F f)
             len -= R;
         }
     }
-    return valid;
 }
 
 __device__ __forceinline__ int chunk_valid(int p0, int L) { return min(kChunk, L - p0); }
 
+__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+__device__ __forceinline__ void sts32(uint8_t* p, uint32_t v) { *reinterpret_cast<uint32_t*>(p) = v; }
+__device__ __forceinline__ void sts64(uint8_t* p, float x, float y) { *reinterpret_cast<float2*>(p) = make_float2(x, y); }
+
 // ------------------------------------------------------------------------------------------
 // Gate math for one chunk (all 128 compute threads).  Thread (w, l) owns logical rows
 // 16w..16w+15 and channels 2l, 2l+1.  Logical row = position inside the chunk along the scan;
-// physical (shared-memory / TMEM) row is mirrored for reversed scans.
-template <bool kStateOnly>
-__device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, int n, int valid, int w, int l) {
+// the physical (shared-memory / TMEM) row is mirrored for reversed scans.  Tiles are rows of
+// 128 bytes whose 16-byte units are XOR-swizzled with (row & 7); since 16w is a multiple of 8
+// the swizzle of logical row i depends on i only, which is a compile-time constant here.
+__device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, int valid, int w, int l,
+                                          bool state_only) {
     const Params& P = *c.p;
     Misc& M = *c.misc;
-    const uint32_t tq = stage + 0 * kTileBytes, tk = stage + 1 * kTileBytes, tg = stage + 2 * kTileBytes,
-                   tv = stage + 3 * kTileBytes;
-    const uint32_t c0 = 2u * l;
     const int par = n & 1;
     const bool rev = P.rev != 0;
+    // byte offset of (logical row 16w+i, channel 2l) in an fp16 tile = row0 + i*step + ((lx ^ (i&7)) << 4) + lb
+    const int row0 = rev ? (63 - 16 * w) * 128 : (16 * w) * 128;
+    const int step = rev ? -128 : 128;
+    const uint32_t lx = rev ? ((l >> 2) ^ 7u) : (l >> 2);
+    const uint32_t lb = (l & 3u) << 2;
+    // tf32 tiles: channel 2l lives in half (l >> 4), 16-byte unit (l & 15) >> 1, byte (l & 1) * 8
+    const uint32_t ly = rev ? (((l & 15u) >> 1) ^ 7u) : ((l & 15u) >> 1);
+    const uint32_t lb32 = (l >> 4) * kTileBytes + ((l & 1u) << 3);
+    uint8_t* tq = stage;
+    uint8_t* tk = stage + kTileBytes;
+    uint8_t* tg = stage + 2 * kTileBytes;
+    uint8_t* tv = stage + 3 * kTileBytes;
+    uint8_t* qbar = c.base + kOffQbar;
+    uint8_t* kbar = c.base + kOffKbar;
+    const uint32_t c0 = 2u * l;
+#define GLA_OFF16(i) (row0 + (i) * step + static_cast<int>(((lx ^ ((i) & 7u)) << 4) + lb))
+#define GLA_OFF32(i) (row0 + (i) * step + static_cast<int>(((ly ^ ((i) & 7u)) << 4) + lb32))
 
     float cs0[16], cs1[16];
-    float a0 = 0.f, a1 = 0.f;
+    {
+        uint32_t graw[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const int lam = 16 * w + i;
-        const uint32_t rho = rev ? 63 - lam : lam;
-        float2 gv = make_float2(0.f, 0.f);
-        if (lam < valid) {
-            gv = unpack_half2(ld_shared_u32(tg + sw_f16(rho, c0)));
+        for (int i = 0; i < 16; ++i) graw[i] = lds32(tg + GLA_OFF16(i));
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float2 gv = unpack_half2(graw[i]);
             if (P.inv_norm > 0.f) {
                 gv.x = logsigmoid_f(gv.x) * P.inv_norm;
                 gv.y = logsigmoid_f(gv.y) * P.inv_norm;
             }
+            const bool live = 16 * w + i < valid;
+            a0 += live ? gv.x * kLog2e : 0.f;
+            a1 += live ? gv.y * kLog2e : 0.f;
+            cs0[i] = a0;
+            cs1[i] = a1;
         }
-        a0 += gv.x;
-        a1 += gv.y;
-        cs0[i] = a0;
-        cs1[i] = a1;
+        *reinterpret_cast<float2*>(&M.tot[par][w][c0]) = make_float2(a0, a1);
     }
-    M.tot[par][w][c0] = a0;
-    M.tot[par][w][c0 + 1] = a1;
     named_bar_sync(1, kComputeThreads);
     float off0 = 0.f, off1 = 0.f, b40 = 0.f, b41 = 0.f, gm0 = 0.f, gm1 = 0.f;
 #pragma unroll
     for (int ww = 0; ww < 4; ++ww) {
-        const float t0 = M.tot[par][ww][c0], t1 = M.tot[par][ww][c0 + 1];
-        if (ww < w) { off0 += t0; off1 += t1; }
-        if (ww < 2) { gm0 += t0; gm1 += t1; }
-        b40 += t0;
-        b41 += t1;
+        const float2 t = *reinterpret_cast<const float2*>(&M.tot[par][ww][c0]);
+        if (ww < w) { off0 += t.x; off1 += t.y; }
+        if (ww < 2) { gm0 += t.x; gm1 += t.y; }
+        b40 += t.x;
+        b41 += t.y;
     }
-    if (w == 0) {
-        M.b4s[par][c0] = b40;
-        M.b4s[par][c0 + 1] = b41;
-    }
+    if (w == 0) *reinterpret_cast<float2*>(&M.b4s[par][c0]) = make_float2(b40, b41);
     bool wide = false;
     float e10 = 0.f, e11 = 0.f, e20 = 0.f, e21 = 0.f;
-    if (!kStateOnly) {
+    if (!state_only) {
         wide = __any_sync(0xffffffffu, (-b40 > kWideLimit) || (-b41 > kWideLimit));
         if (w == 0 && l == 0) M.wide[par] = wide ? 1u : 0u;
-        if (!wide) {
-            e10 = fast_exp(-gm0);
-            e11 = fast_exp(-gm1);
-            e20 = fast_exp(gm0 - b40);
-            e21 = fast_exp(gm1 - b41);
-        }
+        e10 = ex2(-gm0);
+        e11 = ex2(-gm1);
+        e20 = ex2(gm0 - b40);
+        e21 = ex2(gm1 - b41);
     }
-    const uint32_t qbar = c.smem + kOffQbar, kbar = c.smem + kOffKbar;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const int lam = 16 * w + i;
-        const uint32_t rho = rev ? 63 - lam : lam;
-        const uint32_t a16 = sw_f16(rho, c0);
-        if (lam < valid) {
+    for (int half = 0; half < 2; ++half) {
+        uint32_t kraw[8], qraw[8];
+#pragma unroll
+        for (int ii = 0; ii < 8; ++ii) {
+            const int i = 8 * half + ii;
+            kraw[ii] = lds32(tk + GLA_OFF16(i));
+            qraw[ii] = state_only ? 0u : lds32(tq + GLA_OFF16(i));
+        }
+#pragma unroll
+        for (int ii = 0; ii < 8; ++ii) {
+            const int i = 8 * half + ii;
+            const bool live = 16 * w + i < valid;
             const float G0 = off0 + cs0[i], G1 = off1 + cs1[i];
-            const uint32_t kraw = ld_shared_u32(tk + a16);
-            const float2 kv = unpack_half2(kraw);
-            const float kh0 = kv.x * fast_exp(b40 - G0), kh1 = kv.y * fast_exp(b41 - G1);
-            st_shared_u32(tk + a16, pack_half2_sat(kh0, kh1));
-            if (!kStateOnly) {
-                const uint32_t qraw = ld_shared_u32(tq + a16);
-                const float2 qv = unpack_half2(qraw);
-                const float qh0 = qv.x * fast_exp(G0), qh1 = qv.y * fast_exp(G1);
-                st_shared_u32(tq + a16, pack_half2_sat(qh0, qh1));
+            const uint32_t kr = live ? kraw[ii] : 0u, qr = live ? qraw[ii] : 0u;
+            const float2 kv = unpack_half2(kr);
+            const float kh0 = kv.x * ex2(b40 - G0), kh1 = kv.y * ex2(b41 - G1);
+            sts32(tk + GLA_OFF16(i), pack_half2_sat(kh0, kh1));
+            if (!live) sts32(tv + GLA_OFF16(i), 0u);   // rows past the end must be finite for the MMAs
+            if (!state_only) {
+                const float2 qv = unpack_half2(qr);
+                const float qh0 = qv.x * ex2(G0), qh1 = qv.y * ex2(G1);
+                sts32(tq + GLA_OFF16(i), pack_half2_sat(qh0, qh1));
                 if (!wide) {
-                    const uint32_t a32 = sw_f32(rho, c0);
-                    st_shared_f2(qbar + a32, to_tf32(qh0 * e10), to_tf32(qh1 * e11));
-                    st_shared_f2(kbar + a32, to_tf32(kh0 * e20), to_tf32(kh1 * e21));
+                    sts64(qbar + GLA_OFF32(i), round_tf32(qh0 * e10), round_tf32(qh1 * e11));
+                    sts64(kbar + GLA_OFF32(i), round_tf32(kh0 * e20), round_tf32(kh1 * e21));
                 } else {  // exact path operands, plain layouts: G fp32 [64][64]; raw q, k fp16 [64][64]
-                    st_shared_f2(qbar + rho * 256u + c0 * 4u, G0, G1);
-                    st_shared_u32(kbar + rho * 128u + c0 * 2u, qraw);
-                    st_shared_u32(kbar + kTileBytes + rho * 128u + c0 * 2u, kraw);
-                }
-            }
-        } else {  // beyond the end of the sequence: contributes nothing, and must be finite for the MMAs
-            st_shared_u32(tk + a16, 0u);
-            st_shared_u32(tv + a16, 0u);
-            if (!kStateOnly) {
-                st_shared_u32(tq + a16, 0u);
-                if (!wide) {
-                    const uint32_t a32 = sw_f32(rho, c0);
-                    st_shared_f2(qbar + a32, 0.f, 0.f);
-                    st_shared_f2(kbar + a32, 0.f, 0.f);
-                } else {
-                    st_shared_f2(qbar + rho * 256u + c0 * 4u, b40, b41);
-                    st_shared_u32(kbar + rho * 128u + c0 * 2u, 0u);
-                    st_shared_u32(kbar + kTileBytes + rho * 128u + c0 * 2u, 0u);
+                    const int rho = rev ? 63 - (16 * w + i) : 16 * w + i;
+                    sts64(qbar + rho * 256 + c0 * 4, G0, G1);
+                    sts32(kbar + rho * 128 + c0 * 2, qr);
+                    sts32(kbar + kTileBytes + rho * 128 + c0 * 2, kr);
                 }
             }
         }
     }
+#undef GLA_OFF16
+#undef GLA_OFF32
     fence_proxy_async_smem();
 }
 
+__device__ __forceinline__ uint32_t sw_f16(uint32_t row, uint32_t col) {     // col in fp16 elements
+    return row * 128u + ((((col >> 3) ^ row) & 7u) << 4) + ((col & 7u) << 1);
+}
+
 // Exact intra-chunk scores for chunks whose gates are too strong for a common reference:
-// A[i][j] = sum_c q[i][c] k[j][c] exp(G[i][c] - G[j][c]) for j at or before i along the scan.
-__device__ __forceinline__ void exact_scores(const Ctx& c, uint32_t a16_tile, int tid) {
+// A[i][j] = sum_c q[i][c] k[j][c] 2^(G[i][c] - G[j][c]) for j at or before i along the scan.
+__device__ __noinline__ void exact_scores(const Ctx& c, uint8_t* a16_tile, int tid) {
     const bool rev = c.p->rev != 0;
-    const uint32_t gs = c.smem + kOffQbar, qs = c.smem + kOffKbar, ks = qs + kTileBytes;
+    const uint8_t* gs = c.base + kOffQbar;
+    const uint8_t* qs = c.base + kOffKbar;
+    const uint8_t* ks = qs + kTileBytes;
     const uint32_t i = tid >> 1;
     for (uint32_t j = tid & 1; j < 64; j += 2) {
         float s = 0.f;
         const bool keep = rev ? (j >= i) : (j <= i);
         if (keep) {
             for (uint32_t ch = 0; ch < 64; ch += 2) {
-                const float2 gi = ld_shared_f2(gs + i * 256u + ch * 4u);
-                const float2 gj = ld_shared_f2(gs + j * 256u + ch * 4u);
-                const float2 qv = unpack_half2(ld_shared_u32(qs + i * 128u + ch * 2u));
-                const float2 kv = unpack_half2(ld_shared_u32(ks + j * 128u + ch * 2u));
-                s += qv.x * kv.x * __expf(gi.x - gj.x);
-                s += qv.y * kv.y * __expf(gi.y - gj.y);
+                const float2 gi = *reinterpret_cast<const float2*>(gs + i * 256u + ch * 4u);
+                const float2 gj = *reinterpret_cast<const float2*>(gs + j * 256u + ch * 4u);
+                const float2 qv = unpack_half2(lds32(qs + i * 128u + ch * 2u));
+                const float2 kv = unpack_half2(lds32(ks + j * 128u + ch * 2u));
+                s += qv.x * kv.x * ex2(gi.x - gj.x);
+                s += qv.y * kv.y * ex2(gi.y - gj.y);
             }
         }
         const __half hv = __float2half_rn(fminf(fmaxf(s, -65504.f), 65504.f));
-        st_shared_u16(a16_tile + sw_f16(i, j), __half_as_ushort(hv));
+        *reinterpret_cast<__half*>(a16_tile + sw_f16(i, j)) = hv;
     }
 }
 
-// Read this thread's TMEM lane (64 fp32 columns starting at `col`).
-__device__ __forceinline__ void tmem_row64(uint32_t tmem_base, int w, uint32_t col, float* x) {
+// Read `N` consecutive fp32 columns of this thread's TMEM lane (N = 32 or 64).
+template <int N>
+__device__ __forceinline__ void tmem_row(uint32_t tmem_base, int w, uint32_t col, float* x) {
     const uint32_t addr = tmem_base + (static_cast<uint32_t>(32 * w) << 16) + col;
     uint32_t* r = reinterpret_cast<uint32_t*>(x);
     __syncwarp();   // tcgen05.ld is warp-collective; lane 0 may come from a single-thread branch
-    tmem_ld16(addr, r);
-    tmem_ld16(addr + 16, r + 16);
-    tmem_ld16(addr + 32, r + 32);
-    tmem_ld16(addr + 48, r + 48);
+#pragma unroll
+    for (int k = 0; k < N / 16; ++k) tmem_ld16(addr + 16 * k, r + 16 * k);
     tmem_ld_wait();
 }
 
-// Write 64 floats as one fp16 row of a swizzled tile.
-__device__ __forceinline__ void store_row_f16(uint32_t tile, uint32_t row, const float* x) {
+// Write 8*N8 floats as fp16 into 16-byte units unit0.. of one row of a swizzled tile.
+template <int N8>
+__device__ __forceinline__ void store_row_f16(uint8_t* tile, uint32_t row, uint32_t unit0, const float* x) {
 #pragma unroll
-    for (uint32_t m = 0; m < 8; ++m) {
-        const uint32_t a = tile + row * 128u + (((m ^ row) & 7u) << 4);
-        st_shared_v4(a, pack_half2_sat(x[8 * m], x[8 * m + 1]), pack_half2_sat(x[8 * m + 2], x[8 * m + 3]),
-                     pack_half2_sat(x[8 * m + 4], x[8 * m + 5]), pack_half2_sat(x[8 * m + 6], x[8 * m + 7]));
+    for (uint32_t m = 0; m < N8; ++m) {
+        uint8_t* a = tile + row * 128u + ((((unit0 + m) ^ row) & 7u) << 4);
+        *reinterpret_cast<uint4*>(a) =
+            make_uint4(pack_half2_sat(x[8 * m], x[8 * m + 1]), pack_half2_sat(x[8 * m + 2], x[8 * m + 3]),
+                       pack_half2_sat(x[8 * m + 4], x[8 * m + 5]), pack_half2_sat(x[8 * m + 6], x[8 * m + 7]));
     }
 }
 
@@ -338,6 +360,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     Ctx ctx;
     ctx.p = &P;
     ctx.misc = &M;
+    ctx.base = base_ptr;
     ctx.smem = base;
     ctx.deadline_span_ns = static_cast<uint64_t>(P.wait_limit_us) * 1000ull;
 
@@ -349,9 +372,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         mbar_init(smem_u32(&M.ops_ready), kComputeThreads);
         mbar_init(smem_u32(&M.a_done), 1);
         mbar_init(smem_u32(&M.a16_ready), kComputeThreads);
-        mbar_init(smem_u32(&M.o_done), 1);
-        mbar_init(smem_u32(&M.o_free), kComputeThreads);
-        mbar_init(smem_u32(&M.s_done), 1);
+        mbar_init(smem_u32(&M.os_done), 1);
+        mbar_init(smem_u32(&M.acc_free), kComputeThreads);
         mbar_init(smem_u32(&M.s16_ready), kComputeThreads);
         M.abort = 0;
         fence_mbar_init();
@@ -369,15 +391,14 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = M.tmem_base;
-    const uint32_t tmA = tmem + 0, tmO = tmem + 64, tmS = tmem + 128;
 
     // use counters of every barrier, kept per role (all roles see the same sequence of uses)
     uint32_t n_full[kNumStages] = {0, 0}, n_empty[kNumStages] = {0, 0};
-    uint32_t n_ops = 0, n_adone = 0, n_a16 = 0, n_odone = 0, n_ofree = 0, n_sdone = 0, n_s16 = 0;
+    uint32_t n_ops = 0, n_adone = 0, n_a16 = 0, n_osdone = 0, n_accfree = 0, n_s16 = 0;
     uint32_t chunk_ctr = 0;   // chunks processed by this CTA so far: stage = ctr % 2, parity slot = ctr & 1
 
-    float S[kD];              // fp32 state row of channel 16w+l (lanes 0..15 of each compute warp)
-    const bool owner = (w < 4) && (l < 16);
+    float S[kD];              // lanes 16-31 of compute warp w: fp32 state row of channel 16w + l - 16
+    const bool owner = (w < 4) && (l >= 16);
     const int my_c = 16 * (w & 3) + (l & 15);
 
     while (true) {
@@ -418,9 +439,10 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         } else if (w == 5) {
             // ------------------------------------------------------------ MMA issue
             if (l == 0) {
-                constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 64);
-                constexpr uint32_t idO1 = umma_idesc(FMT_F16, 0, 1, 64, 64);
+                constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 32);
+                constexpr uint32_t idO = umma_idesc(FMT_F16, 0, 1, 64, 64);
                 constexpr uint32_t idS = umma_idesc(FMT_F16, 1, 1, 64, 64);
+                const uint32_t tmA = tmem + kTmA, tmO = tmem + kTmOS, tmS = tmem + kTmOS + kLane16;
                 uint32_t ctr = chunk_ctr;
                 for (int pass = 0; pass < npass; ++pass) {
                     const bool state_only = it.state_pass && pass == 0;
@@ -437,31 +459,34 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
 #pragma unroll
                                 for (uint32_t ks = 0; ks < 8; ++ks) {
                                     const uint32_t o = (ks >> 2) * kTileBytes + (ks & 3) * 32u;
-                                    umma_tf32(tmA, umma_desc_sw128(base + kOffQbar + o),
-                                              umma_desc_sw128(base + kOffKbar + o), idA, ks);
+                                    const uint64_t da = umma_desc_sw128(base + kOffQbar + o);
+                                    umma_tf32(tmA, da, umma_desc_sw128(base + kOffKbar + o), idA, ks);
+                                    umma_tf32(tmA + kLane16, da, umma_desc_sw128(base + kOffKbar + o + 32 * 128), idA, ks);
                                 }
                             }
                             umma_commit(smem_u32(&M.a_done));
                             mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
-                            mbar_wait(ctx, &M.o_free, (n_ofree++ & 1u) ^ 1u);
-                            tc_fence_after();
+                        }
+                        // both accumulators of the O/S columns must have been read by the epilogue
+                        mbar_wait(ctx, &M.acc_free, (n_accfree++ & 1u) ^ 1u);
+                        tc_fence_after();
+                        if (!state_only) {
 #pragma unroll
                             for (uint32_t ks = 0; ks < 4; ++ks)
                                 umma_f16(tmO, umma_desc_sw128(tq + ks * 32u),
-                                         umma_desc_sw128(base + kOffS16 + ks * 2048u, 8192), idO1, ks);
+                                         umma_desc_sw128(base + kOffS16 + ks * 2048u, 8192), idO, ks);
                             mbar_wait(ctx, &M.a16_ready, n_a16++ & 1u);
                             tc_fence_after();
 #pragma unroll
                             for (uint32_t ks = 0; ks < 4; ++ks)
                                 umma_f16(tmO, umma_desc_sw128(ta16 + ks * 32u),
-                                         umma_desc_sw128(tv + ks * 2048u, 8192), idO1, 1);
-                            umma_commit(smem_u32(&M.o_done));
+                                         umma_desc_sw128(tv + ks * 2048u, 8192), idO, 1);
                         }
 #pragma unroll
                         for (uint32_t ks = 0; ks < 4; ++ks)
                             umma_f16(tmS, umma_desc_sw128(tk + ks * 2048u, 8192),
                                      umma_desc_sw128(tv + ks * 2048u, 8192), idS, ks);
-                        umma_commit(smem_u32(&M.s_done));
+                        umma_commit(smem_u32(&M.os_done));
                     }
                 }
             }
@@ -470,8 +495,9 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             // ------------------------------------------------------------ compute warps
             const size_t srow = (static_cast<size_t>(it.seq) * kD + my_c) * kD;   // row of a [B,H,K,V] state
             const size_t slot = static_cast<size_t>(it.seq) * P.NS + it.seg;
+            const uint32_t rho = 16 * w + (l & 15);   // O row (lanes 0-15) or state row (lanes 16-31)
             uint32_t ctr = chunk_ctr;
-            float gsum = 0.f;       // log of the segment's total decay for channel my_c
+            float gsum = 0.f;       // log2 of the segment's total decay for channel my_c
 
             auto load_initial = [&]() {
 #pragma unroll
@@ -485,226 +511,174 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     }
                 }
             };
-
-            if (it.state_pass) {
-                // ---------------- pass 1: reduce the segment to (decay, increment)
-                if (it.seg == 0) load_initial();
-                else {
-#pragma unroll
-                    for (int x = 0; x < kD; ++x) S[x] = 0.f;
-                }
-                {
-                    const uint32_t s = ctr % kNumStages;
-                    mbar_wait(ctx, &M.full[s], n_full[s]++ & 1u);
-                    gate_math<true>(ctx, base + kOffStage + s * kStageBytes, ctr,
-                                    chunk_valid(it.first_chunk * kChunk, P.T), w, l);
-                    mbar_arrive(smem_u32(&M.ops_ready));
-                }
-                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                    const uint32_t s = ctr % kNumStages;
-                    if (i + 1 < it.nchunks) {
-                        const uint32_t s1 = (ctr + 1) % kNumStages;
-                        mbar_wait(ctx, &M.full[s1], n_full[s1]++ & 1u);
-                        gate_math<true>(ctx, base + kOffStage + s1 * kStageBytes, ctr + 1,
-                                        chunk_valid((it.first_chunk + i + 1) * kChunk, P.T), w, l);
-                    }
-                    mbar_wait(ctx, &M.s_done, n_sdone++ & 1u);
-                    tc_fence_after();
-                    float x[kD];
-                    tmem_row64(tmem, w, 128, x);
-                    const float b4 = M.b4s[ctr & 1][my_c];
-                    const float dec = fast_exp(b4);
-                    gsum += b4;
-#pragma unroll
-                    for (int v = 0; v < kD; ++v) S[v] = fmaf(dec, S[v], x[v]);
-                    tc_fence_before();
-                    if (tid == 0) mbar_arrive(smem_u32(&M.empty[s]));
-                    if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.ops_ready));
-                }
-                // ---------------- publish, look back, publish the inclusive state
-                float* my_agg = P.agg + slot * kAggStride;
-                float* my_incl = P.incl + slot * (kD * kD);
-                if (it.seg == 0) {
-                    if (owner) {
-                        float4* dst = reinterpret_cast<float4*>(my_incl + my_c * kD);
-#pragma unroll
-                        for (int x4 = 0; x4 < kD / 4; ++x4)
-                            dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
-                    }
-                    __threadfence();
-                    named_bar_sync(1, kComputeThreads);
-                    if (tid == 0) st_release_gpu(P.flags + slot, 2u);
-                    load_initial();
-                } else {
-                    if (owner) {
-                        float4* dst = reinterpret_cast<float4*>(my_agg + my_c * kD);
-#pragma unroll
-                        for (int x4 = 0; x4 < kD / 4; ++x4)
-                            dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
-                        my_agg[kD * kD + my_c] = gsum;
-                    }
-                    __threadfence();
-                    named_bar_sync(1, kComputeThreads);
-                    if (tid == 0) st_release_gpu(P.flags + slot, 1u);
-                }
-            } else if (it.seg == 0) {
-                load_initial();
-            }
-            if (it.seg > 0) {
-                // decoupled look-back: S <- state entering this segment
-#pragma unroll
-                for (int x = 0; x < kD; ++x) S[x] = 0.f;
-                float dlog = 0.f;
-                int j = it.seg - 1;
-                const uint64_t t0 = globaltimer_ns();
-                while (true) {
-                    const size_t sj = static_cast<size_t>(it.seq) * P.NS + j;
-                    uint32_t f = ld_acquire_gpu(P.flags + sj);
-                    while (f == 0u) {
-                        if (M.abort || ld_acquire_gpu(P.ctrl + 1) != 0u) break;
-                        if (globaltimer_ns() - t0 > ctx.deadline_span_ns) {
-                            raise_timeout(ctx, WHERE_LOOKBACK);
-                            break;
-                        }
-                        __nanosleep(64);
-                        f = ld_acquire_gpu(P.flags + sj);
-                    }
-                    // one decision per warp: the inclusive state only if every lane has seen it published
-                    const bool gave_up = __any_sync(0xffffffffu, f == 0u);
-                    const bool inclusive = __all_sync(0xffffffffu, f == 2u);
-                    if (gave_up) break;   // result undefined, status word set
-                    const float dacc = fast_exp(dlog);
-                    if (inclusive) {
-                        if (owner) {
-                            const float4* src = reinterpret_cast<const float4*>(P.incl + sj * (kD * kD) + my_c * kD);
-#pragma unroll
-                            for (int x4 = 0; x4 < kD / 4; ++x4) {
-                                const float4 v4 = __ldcg(src + x4);
-                                S[4 * x4] = fmaf(dacc, v4.x, S[4 * x4]);
-                                S[4 * x4 + 1] = fmaf(dacc, v4.y, S[4 * x4 + 1]);
-                                S[4 * x4 + 2] = fmaf(dacc, v4.z, S[4 * x4 + 2]);
-                                S[4 * x4 + 3] = fmaf(dacc, v4.w, S[4 * x4 + 3]);
-                            }
-                        }
-                        break;
-                    }
-                    if (owner) {
-                        const float* aj = P.agg + sj * kAggStride;
-                        const float4* src = reinterpret_cast<const float4*>(aj + my_c * kD);
-#pragma unroll
-                        for (int x4 = 0; x4 < kD / 4; ++x4) {
-                            const float4 v4 = __ldcg(src + x4);
-                            S[4 * x4] = fmaf(dacc, v4.x, S[4 * x4]);
-                            S[4 * x4 + 1] = fmaf(dacc, v4.y, S[4 * x4 + 1]);
-                            S[4 * x4 + 2] = fmaf(dacc, v4.z, S[4 * x4 + 2]);
-                            S[4 * x4 + 3] = fmaf(dacc, v4.w, S[4 * x4 + 3]);
-                        }
-                        dlog += __ldcg(aj + kD * kD + my_c);
-                    }
-                    --j;   // j >= 0 always holds here: segment 0 only ever publishes an inclusive state
-                    if (j < 0) break;
-                }
-                if (it.state_pass) {
-                    // inclusive state after this segment = decay * incoming + increment
-                    if (owner) {
-                        const float dseg = fast_exp(gsum);
-                        const float4* inc = reinterpret_cast<const float4*>(P.agg + slot * kAggStride + my_c * kD);
-                        float4* dst = reinterpret_cast<float4*>(P.incl + slot * (kD * kD) + my_c * kD);
-#pragma unroll
-                        for (int x4 = 0; x4 < kD / 4; ++x4) {
-                            const float4 a4 = __ldcg(inc + x4);
-                            dst[x4] = make_float4(fmaf(dseg, S[4 * x4], a4.x), fmaf(dseg, S[4 * x4 + 1], a4.y),
-                                                  fmaf(dseg, S[4 * x4 + 2], a4.z), fmaf(dseg, S[4 * x4 + 3], a4.w));
-                        }
-                    }
-                    __threadfence();
-                    named_bar_sync(1, kComputeThreads);
-                    if (tid == 0) st_release_gpu(P.flags + slot, 2u);
-                }
-            }
-
-            // ---------------- pass 2: outputs
-            if (owner) store_row_f16(base + kOffS16, my_c, S);
-            fence_proxy_async_smem();
-            mbar_arrive(smem_u32(&M.s16_ready));
-            {
-                const uint32_t s = ctr % kNumStages;
-                mbar_wait(ctx, &M.full[s], n_full[s]++ & 1u);
-                gate_math<false>(ctx, base + kOffStage + s * kStageBytes, ctr,
-                                 chunk_valid(it.first_chunk * kChunk, P.T), w, l);
-                mbar_arrive(smem_u32(&M.ops_ready));
-            }
-            for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                const uint32_t s = ctr % kNumStages;
-                const uint32_t stage = base + kOffStage + s * kStageBytes;
-                const uint32_t rho = 16 * w + (l & 15);
-                float x[kD];
-                // scores: TMEM -> causal mask -> fp16 tile (takes the place of the raw gate tile)
-                mbar_wait(ctx, &M.a_done, n_adone++ & 1u);
-                tc_fence_after();
-                if (!M.wide[ctr & 1]) {
-                    tmem_row64(tmem, w, 0, x);
-                    if (owner) {
-#pragma unroll
-                        for (uint32_t j = 0; j < kD; ++j) {
-                            const bool keep = P.rev ? (j >= rho) : (j <= rho);
-                            x[j] = keep ? x[j] : 0.f;
-                        }
-                        store_row_f16(stage + 2 * kTileBytes, rho, x);
-                    }
-                } else {
-                    named_bar_sync(1, kComputeThreads);
-                    exact_scores(ctx, stage + 2 * kTileBytes, tid);
-                }
-                fence_proxy_async_smem();
-                tc_fence_before();
-                mbar_arrive(smem_u32(&M.a16_ready));
-                // gate math of the next chunk overlaps the A.V and state MMAs of this one
-                if (i + 1 < it.nchunks) {
-                    const uint32_t s1 = (ctr + 1) % kNumStages;
-                    mbar_wait(ctx, &M.full[s1], n_full[s1]++ & 1u);
-                    gate_math<false>(ctx, base + kOffStage + s1 * kStageBytes, ctr + 1,
-                                     chunk_valid((it.first_chunk + i + 1) * kChunk, P.T), w, l);
-                    mbar_arrive(smem_u32(&M.ops_ready));
-                }
-                // outputs: TMEM -> scale -> fp16 tile (takes the place of qh) -> TMA store
-                mbar_wait(ctx, &M.o_done, n_odone++ & 1u);
-                tc_fence_after();
-                tmem_row64(tmem, w, 64, x);
-                tc_fence_before();
-                mbar_arrive(smem_u32(&M.o_free));
+            auto publish = [&](float* dst_row, uint32_t flag_value) {
                 if (owner) {
+                    float4* dst = reinterpret_cast<float4*>(dst_row);
 #pragma unroll
-                    for (int v = 0; v < kD; ++v) x[v] *= P.scale;
-                    store_row_f16(stage, rho, x);
+                    for (int x4 = 0; x4 < kD / 4; ++x4)
+                        dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
                 }
-                fence_proxy_async_smem();
+                __threadfence();
                 named_bar_sync(1, kComputeThreads);
-                if (tid == 0) {
-                    const int p0 = (it.first_chunk + i) * kChunk;
-                    for_each_box(p0, P.T, P.Hc, P.rev, [&](int id, int r, int c, int row) {
-                        tma_store_5d(&maps.m[TO][id], stage + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
-                    });
-                    tma_store_commit();
-                }
-                // state: S <- exp(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
-                mbar_wait(ctx, &M.s_done, n_sdone++ & 1u);
-                tc_fence_after();
-                tmem_row64(tmem, w, 128, x);
-                tc_fence_before();
-                {
-                    const float dec = fast_exp(M.b4s[ctr & 1][my_c]);
+                if (tid == 0) st_release_gpu(P.flags + slot, flag_value);
+            };
+
+            for (int pass = 0; pass < npass; ++pass) {
+                const bool state_only = it.state_pass && pass == 0;
+                if (state_only) {
+                    // pass 1 reduces the segment to (decay, increment); segment 0 folds the initial state in
+                    if (it.seg == 0) load_initial();
+                    else {
 #pragma unroll
-                    for (int v = 0; v < kD; ++v) S[v] = fmaf(dec, S[v], x[v]);
-                }
-                if (i + 1 < it.nchunks) {
-                    if (owner) store_row_f16(base + kOffS16, my_c, S);
+                        for (int x = 0; x < kD; ++x) S[x] = 0.f;
+                    }
+                } else {
+                    if (it.seg == 0) load_initial();
+                    else {
+                        // decoupled look-back: S <- state entering this segment
+#pragma unroll
+                        for (int x = 0; x < kD; ++x) S[x] = 0.f;
+                        float dlog = 0.f;
+                        int j = it.seg - 1;
+                        const uint64_t t0 = globaltimer_ns();
+                        while (true) {
+                            const size_t sj = static_cast<size_t>(it.seq) * P.NS + j;
+                            uint32_t f = ld_acquire_gpu(P.flags + sj);
+                            while (f == 0u) {
+                                if (M.abort || ld_acquire_gpu(P.ctrl + 1) != 0u) break;
+                                if (globaltimer_ns() - t0 > ctx.deadline_span_ns) {
+                                    raise_timeout(ctx, WHERE_LOOKBACK);
+                                    break;
+                                }
+                                __nanosleep(64);
+                                f = ld_acquire_gpu(P.flags + sj);
+                            }
+                            // one decision per warp: the inclusive state only if every lane has seen it published
+                            const bool gave_up = __any_sync(0xffffffffu, f == 0u);
+                            const bool inclusive = __all_sync(0xffffffffu, f == 2u);
+                            if (gave_up) break;   // result undefined, status word set
+                            const float dacc = ex2(dlog);
+                            const float* src_row = inclusive ? P.incl + sj * (kD * kD) + my_c * kD
+                                                             : P.agg + sj * kAggStride + my_c * kD;
+                            if (owner) {
+                                const float4* src = reinterpret_cast<const float4*>(src_row);
+#pragma unroll
+                                for (int x4 = 0; x4 < kD / 4; ++x4) {
+                                    const float4 v4 = __ldcg(src + x4);
+                                    S[4 * x4] = fmaf(dacc, v4.x, S[4 * x4]);
+                                    S[4 * x4 + 1] = fmaf(dacc, v4.y, S[4 * x4 + 1]);
+                                    S[4 * x4 + 2] = fmaf(dacc, v4.z, S[4 * x4 + 2]);
+                                    S[4 * x4 + 3] = fmaf(dacc, v4.w, S[4 * x4 + 3]);
+                                }
+                                if (!inclusive) dlog += __ldcg(P.agg + sj * kAggStride + kD * kD + my_c);
+                            }
+                            if (inclusive) break;
+                            --j;   // never drops below 0: segment 0 only ever publishes an inclusive state
+                            if (j < 0) break;
+                        }
+                        if (it.state_pass) {
+                            // inclusive state after this segment = decay * incoming + increment
+                            if (owner) {
+                                const float dseg = ex2(gsum);
+                                const float4* inc = reinterpret_cast<const float4*>(P.agg + slot * kAggStride + my_c * kD);
+                                float4* dst = reinterpret_cast<float4*>(P.incl + slot * (kD * kD) + my_c * kD);
+#pragma unroll
+                                for (int x4 = 0; x4 < kD / 4; ++x4) {
+                                    const float4 a4 = __ldcg(inc + x4);
+                                    dst[x4] = make_float4(fmaf(dseg, S[4 * x4], a4.x), fmaf(dseg, S[4 * x4 + 1], a4.y),
+                                                          fmaf(dseg, S[4 * x4 + 2], a4.z), fmaf(dseg, S[4 * x4 + 3], a4.w));
+                                }
+                            }
+                            __threadfence();
+                            named_bar_sync(1, kComputeThreads);
+                            if (tid == 0) st_release_gpu(P.flags + slot, 2u);
+                        }
+                    }
+                    if (owner) store_row_f16<8>(base_ptr + kOffS16, rho, 0, S);
                     fence_proxy_async_smem();
                     mbar_arrive(smem_u32(&M.s16_ready));
                 }
-                if (tid == 0) {
-                    tma_store_wait_read();
-                    mbar_arrive(smem_u32(&M.empty[s]));
+
+                // software pipeline over the chunks: scores(i) | gate math(i+1) | outputs+state(i)
+                for (int i = -1; i < it.nchunks; ++i) {
+                    const uint32_t cc = ctr + static_cast<uint32_t>(i);       // running index of chunk i
+                    const uint32_t s = cc % kNumStages;
+                    uint8_t* stage = base_ptr + kOffStage + s * kStageBytes;
+                    if (i >= 0 && !state_only) {
+                        // scores: TMEM -> causal mask -> fp16 tile (takes the place of the raw gate tile)
+                        mbar_wait(ctx, &M.a_done, n_adone++ & 1u);
+                        tc_fence_after();
+                        if (!M.wide[cc & 1]) {
+                            float x[32];
+                            tmem_row<32>(tmem, w, kTmA, x);
+                            const uint32_t j0 = (l >> 4) * 32u;   // lanes 16-31 hold key rows 32-63
+#pragma unroll
+                            for (uint32_t j = 0; j < 32; ++j) {
+                                const bool keep = P.rev ? (j0 + j >= rho) : (j0 + j <= rho);
+                                x[j] = keep ? x[j] : 0.f;
+                            }
+                            store_row_f16<4>(stage + 2 * kTileBytes, rho, j0 >> 3, x);
+                        } else {
+                            named_bar_sync(1, kComputeThreads);
+                            exact_scores(ctx, stage + 2 * kTileBytes, tid);
+                        }
+                        fence_proxy_async_smem();
+                        tc_fence_before();
+                        mbar_arrive(smem_u32(&M.a16_ready));
+                    }
+                    if (i + 1 < it.nchunks) {
+                        const uint32_t s1 = (cc + 1) % kNumStages;
+                        mbar_wait(ctx, &M.full[s1], n_full[s1]++ & 1u);
+                        gate_math(ctx, base_ptr + kOffStage + s1 * kStageBytes, static_cast<int>(cc + 1),
+                                  chunk_valid((it.first_chunk + i + 1) * kChunk, P.T), w, l, state_only);
+                        if (!state_only) mbar_arrive(smem_u32(&M.ops_ready));
+                    }
+                    if (i >= 0) {
+                        // lanes 0-15: outputs -> scale -> fp16 tile (takes the place of qh) -> TMA store
+                        // lanes 16-31: S <- 2^(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
+                        mbar_wait(ctx, &M.os_done, n_osdone++ & 1u);
+                        tc_fence_after();
+                        float x[kD];
+                        tmem_row<kD>(tmem, w, kTmOS, x);
+                        tc_fence_before();
+                        mbar_arrive(smem_u32(&M.acc_free));
+                        const float b4 = M.b4s[cc & 1][my_c];
+                        const float dec = owner ? ex2(b4) : 0.f;
+                        const float mul = owner ? 1.f : P.scale;
+                        if (owner) gsum += b4;
+#pragma unroll
+                        for (int v = 0; v < kD; ++v) {
+                            S[v] = fmaf(dec, S[v], x[v]);
+                            x[v] = S[v] * mul;
+                        }
+                        if (!state_only) {
+                            store_row_f16<8>(owner ? base_ptr + kOffS16 : stage, rho, 0, x);
+                            fence_proxy_async_smem();
+                            if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.s16_ready));
+                            named_bar_sync(1, kComputeThreads);
+                            if (tid == 0) {
+                                const int p0 = (it.first_chunk + i) * kChunk;
+                                const uint32_t st = base + kOffStage + s * kStageBytes;
+                                for_each_box(p0, P.T, P.Hc, P.rev, [&](int id, int r, int c, int row) {
+                                    tma_store_5d(&maps.m[TO][id], st + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
+                                });
+                                tma_store_commit();
+                                tma_store_wait_read();
+                            }
+                        }
+                        if (tid == 0) mbar_arrive(smem_u32(&M.empty[s]));
+                    }
+                    if (state_only && i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.ops_ready));
+                }
+                ctr += static_cast<uint32_t>(it.nchunks);
+
+                if (state_only) {
+                    if (it.seg == 0) {
+                        publish(P.incl + slot * (kD * kD) + my_c * kD, 2u);
+                    } else {
+                        if (owner) P.agg[slot * kAggStride + kD * kD + my_c] = gsum;
+                        publish(P.agg + slot * kAggStride + my_c * kD, 1u);
+                    }
                 }
             }
             if (it.seg == P.NS - 1 && P.sT != nullptr && owner) {

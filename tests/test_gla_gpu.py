@@ -226,7 +226,8 @@ def test_fla_style_call_returns_final_state(G):
 
 def test_round_trip_property_at_full_size(G):
     """Size-independent property at the benchmark shape: running the reversed scan on the
-    token-reversed inputs gives the token-reversed output of the forward scan, bit for bit."""
+    token-reversed inputs gives the token-reversed output of the forward scan (the two runs sum
+    the same products in a different order, so they agree to rounding, not bit for bit)."""
     from oracle import gla_ref
     q, k, v, g = (x.cuda() for x in gla_ref.config_inputs("c3"))
     B, T, H, _ = q.shape
@@ -237,7 +238,9 @@ def test_round_trip_property_at_full_size(G):
     G.chunk_gla_run(q.flip(1).contiguous(), k.flip(1).contiguous(), v.flip(1).contiguous(),
                     g.flip(1).contiguous(), 0.125, ws, o2, direction=1)
     G.check_status(ws)
-    assert torch.equal(o1, o2.flip(1))
+    from oracle import gla_ref as R
+    m = R.error_metrics(o1.float(), o2.flip(1).float())
+    assert m["finite"] and m["rel_l2"] <= 3e-4 and m["max_abs"] <= 1e-4, m
 
 
 def test_rmsnorm_gated(G):
