@@ -26,7 +26,8 @@
 // therefore owns useful data: lanes 0-15 of warp w hold row 16w+l of O (and the left half of
 // A), lanes 16-31 hold state row 16w+l-16 (and the right half of A).
 //
-// Warp roles: warps 0-3 gate math, TMEM epilogues, state; warp 4 TMA producer; warp 5 MMA issue.
+// Warp roles: warps 0-7 gate math, TMEM epilogues, state (warps w and w+4 share TMEM quadrant w
+// and split its columns); warp 8 TMA producer; warp 9 MMA issue.
 #pragma once
 
 #include "gla_device.cuh"
@@ -38,8 +39,11 @@ constexpr int kD = 64;                    // K = V = 64
 constexpr int kTileBytes = kChunk * 128;  // one fp16 [64 x 64] tile
 constexpr int kStageBytes = 4 * kTileBytes;
 constexpr int kNumStages = 2;
-constexpr int kComputeThreads = 128;
-constexpr int kThreads = 192;
+constexpr int kComputeWarps = 8;           // two warps per TMEM lane quadrant, each taking half the columns
+constexpr int kComputeThreads = 32 * kComputeWarps;
+constexpr int kThreads = kComputeThreads + 64;
+constexpr int kRowsPerThread = kChunk / kComputeWarps;   // gate math: logical rows per thread
+constexpr int kColSplit = kComputeWarps / 4;
 constexpr int kTmemCols = 128;
 constexpr uint32_t kTmA = 0;              // scores: 32 columns, two interleaved halves
 constexpr uint32_t kTmOS = 32;            // outputs (lane offset 0) and state increment (lane offset 16)
@@ -83,7 +87,7 @@ constexpr int kOffQbar = kNumStages * kStageBytes;       // 16 KB tf32 (two 8 KB
 constexpr int kOffKbar = kOffQbar + 2 * kTileBytes;
 constexpr int kOffS16 = kOffKbar + 2 * kTileBytes;
 constexpr int kOffMisc = kOffS16 + kTileBytes;
-constexpr int kMiscBytes = 4096;
+constexpr int kMiscBytes = 6144;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + alignment slack
 
 struct Misc {
@@ -94,7 +98,7 @@ struct Misc {
     volatile uint32_t abort;
     int item;
     uint32_t wide[2];
-    alignas(16) float tot[2][4][kD];   // per-warp gate sums of the two chunks in flight (read as float2)
+    alignas(16) float tot[2][kComputeWarps][kD];   // per-warp gate sums of the two chunks in flight (float2 access)
     alignas(16) float b4s[2][kD];      // chunk totals G_L per channel
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "misc block too large");
@@ -165,19 +169,32 @@ __device__ __forceinline__ void sts32(uint8_t* p, uint32_t v) { *reinterpret_cas
 __device__ __forceinline__ void sts64(uint8_t* p, float x, float y) { *reinterpret_cast<float2*>(p) = make_float2(x, y); }
 
 // ------------------------------------------------------------------------------------------
-// Gate math for one chunk (all 128 compute threads).  Thread (w, l) owns logical rows
-// 16w..16w+15 and channels 2l, 2l+1.  Logical row = position inside the chunk along the scan;
+// Raw-logit gates (gk_normalizer > 0): rewrite the gate tile in place as fp16 log gates,
+// logsigmoid(x) / normalizer, before the gate math reads it.  Kept out of line and rolled: it is
+// a rarely used mode and must not bloat the main loop.
+__device__ __noinline__ void logits_to_log_gates(uint8_t* tg, float inv_norm, int tid) {
+    for (int e = tid; e < kChunk * kD / 2; e += kComputeThreads) {
+        uint32_t* p = reinterpret_cast<uint32_t*>(tg) + e;
+        const float2 x = unpack_half2(*p);
+        *p = pack_half2_sat(logsigmoid_f(x.x) * inv_norm, logsigmoid_f(x.y) * inv_norm);
+    }
+}
+
+// Gate math for one chunk (all compute threads).  Thread (w, l) owns logical rows
+// 8w..8w+7 and channels 2l, 2l+1.  Logical row = position inside the chunk along the scan;
 // the physical (shared-memory / TMEM) row is mirrored for reversed scans.  Tiles are rows of
-// 128 bytes whose 16-byte units are XOR-swizzled with (row & 7); since 16w is a multiple of 8
+// 128 bytes whose 16-byte units are XOR-swizzled with (row & 7); since 8w is a multiple of 8
 // the swizzle of logical row i depends on i only, which is a compile-time constant here.
 __device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, int valid, int w, int l,
                                           bool state_only) {
+    constexpr int R = kRowsPerThread;
+    static_assert(R == 8, "the swizzle shortcut below needs 8 rows per thread");
     const Params& P = *c.p;
     Misc& M = *c.misc;
     const int par = n & 1;
     const bool rev = P.rev != 0;
-    // byte offset of (logical row 16w+i, channel 2l) in an fp16 tile = row0 + i*step + ((lx ^ (i&7)) << 4) + lb
-    const int row0 = rev ? (63 - 16 * w) * 128 : (16 * w) * 128;
+    // byte offset of (logical row 8w+i, channel 2l) in an fp16 tile = row0 + i*step + ((lx ^ i) << 4) + lb
+    const int row0 = rev ? (63 - R * w) * 128 : (R * w) * 128;
     const int step = rev ? -128 : 128;
     const uint32_t lx = rev ? ((l >> 2) ^ 7u) : (l >> 2);
     const uint32_t lb = (l & 3u) << 2;
@@ -191,23 +208,28 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, i
     uint8_t* qbar = c.base + kOffQbar;
     uint8_t* kbar = c.base + kOffKbar;
     const uint32_t c0 = 2u * l;
-#define GLA_OFF16(i) (row0 + (i) * step + static_cast<int>(((lx ^ ((i) & 7u)) << 4) + lb))
-#define GLA_OFF32(i) (row0 + (i) * step + static_cast<int>(((ly ^ ((i) & 7u)) << 4) + lb32))
+#define GLA_OFF16(i) (row0 + (i) * step + static_cast<int>(((lx ^ static_cast<uint32_t>(i)) << 4) + lb))
+#define GLA_OFF32(i) (row0 + (i) * step + static_cast<int>(((ly ^ static_cast<uint32_t>(i)) << 4) + lb32))
 
-    float cs0[16], cs1[16];
-    {
-        uint32_t graw[16];
+    if (P.inv_norm > 0.f) {
+        logits_to_log_gates(tg, P.inv_norm, 32 * w + l);
+        named_bar_sync(1, kComputeThreads);
+    }
+    uint32_t graw[R], kraw[R], qraw[R];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) graw[i] = lds32(tg + GLA_OFF16(i));
+    for (int i = 0; i < R; ++i) graw[i] = lds32(tg + GLA_OFF16(i));
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        kraw[i] = lds32(tk + GLA_OFF16(i));
+        qraw[i] = state_only ? 0u : lds32(tq + GLA_OFF16(i));
+    }
+    float cs0[R], cs1[R];
+    {
         float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            float2 gv = unpack_half2(graw[i]);
-            if (P.inv_norm > 0.f) {
-                gv.x = logsigmoid_f(gv.x) * P.inv_norm;
-                gv.y = logsigmoid_f(gv.y) * P.inv_norm;
-            }
-            const bool live = 16 * w + i < valid;
+        for (int i = 0; i < R; ++i) {
+            const float2 gv = unpack_half2(graw[i]);
+            const bool live = R * w + i < valid;
             a0 += live ? gv.x * kLog2e : 0.f;
             a1 += live ? gv.y * kLog2e : 0.f;
             cs0[i] = a0;
@@ -218,10 +240,10 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, i
     named_bar_sync(1, kComputeThreads);
     float off0 = 0.f, off1 = 0.f, b40 = 0.f, b41 = 0.f, gm0 = 0.f, gm1 = 0.f;
 #pragma unroll
-    for (int ww = 0; ww < 4; ++ww) {
+    for (int ww = 0; ww < kComputeWarps; ++ww) {
         const float2 t = *reinterpret_cast<const float2*>(&M.tot[par][ww][c0]);
         if (ww < w) { off0 += t.x; off1 += t.y; }
-        if (ww < 2) { gm0 += t.x; gm1 += t.y; }
+        if (ww < kComputeWarps / 2) { gm0 += t.x; gm1 += t.y; }
         b40 += t.x;
         b41 += t.y;
     }
@@ -237,37 +259,26 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, i
         e21 = ex2(gm1 - b41);
     }
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        uint32_t kraw[8], qraw[8];
-#pragma unroll
-        for (int ii = 0; ii < 8; ++ii) {
-            const int i = 8 * half + ii;
-            kraw[ii] = lds32(tk + GLA_OFF16(i));
-            qraw[ii] = state_only ? 0u : lds32(tq + GLA_OFF16(i));
-        }
-#pragma unroll
-        for (int ii = 0; ii < 8; ++ii) {
-            const int i = 8 * half + ii;
-            const bool live = 16 * w + i < valid;
-            const float G0 = off0 + cs0[i], G1 = off1 + cs1[i];
-            const uint32_t kr = live ? kraw[ii] : 0u, qr = live ? qraw[ii] : 0u;
-            const float2 kv = unpack_half2(kr);
-            const float kh0 = kv.x * ex2(b40 - G0), kh1 = kv.y * ex2(b41 - G1);
-            sts32(tk + GLA_OFF16(i), pack_half2_sat(kh0, kh1));
-            if (!live) sts32(tv + GLA_OFF16(i), 0u);   // rows past the end must be finite for the MMAs
-            if (!state_only) {
-                const float2 qv = unpack_half2(qr);
-                const float qh0 = qv.x * ex2(G0), qh1 = qv.y * ex2(G1);
-                sts32(tq + GLA_OFF16(i), pack_half2_sat(qh0, qh1));
-                if (!wide) {
-                    sts64(qbar + GLA_OFF32(i), round_tf32(qh0 * e10), round_tf32(qh1 * e11));
-                    sts64(kbar + GLA_OFF32(i), round_tf32(kh0 * e20), round_tf32(kh1 * e21));
-                } else {  // exact path operands, plain layouts: G fp32 [64][64]; raw q, k fp16 [64][64]
-                    const int rho = rev ? 63 - (16 * w + i) : 16 * w + i;
-                    sts64(qbar + rho * 256 + c0 * 4, G0, G1);
-                    sts32(kbar + rho * 128 + c0 * 2, qr);
-                    sts32(kbar + kTileBytes + rho * 128 + c0 * 2, kr);
-                }
+    for (int i = 0; i < R; ++i) {
+        const bool live = R * w + i < valid;
+        const float G0 = off0 + cs0[i], G1 = off1 + cs1[i];
+        const uint32_t kr = live ? kraw[i] : 0u, qr = live ? qraw[i] : 0u;
+        const float2 kv = unpack_half2(kr);
+        const float kh0 = kv.x * ex2(b40 - G0), kh1 = kv.y * ex2(b41 - G1);
+        sts32(tk + GLA_OFF16(i), pack_half2_sat(kh0, kh1));
+        if (!live) sts32(tv + GLA_OFF16(i), 0u);   // rows past the end must be finite for the MMAs
+        if (!state_only) {
+            const float2 qv = unpack_half2(qr);
+            const float qh0 = qv.x * ex2(G0), qh1 = qv.y * ex2(G1);
+            sts32(tq + GLA_OFF16(i), pack_half2_sat(qh0, qh1));
+            if (!wide) {
+                sts64(qbar + GLA_OFF32(i), round_tf32(qh0 * e10), round_tf32(qh1 * e11));
+                sts64(kbar + GLA_OFF32(i), round_tf32(kh0 * e20), round_tf32(kh1 * e21));
+            } else {  // exact path operands, plain layouts: G fp32 [64][64]; raw q, k fp16 [64][64]
+                const int rho = rev ? 63 - (R * w + i) : R * w + i;
+                sts64(qbar + rho * 256 + c0 * 4, G0, G1);
+                sts32(kbar + rho * 128 + c0 * 2, qr);
+                sts32(kbar + kTileBytes + rho * 128 + c0 * 2, kr);
             }
         }
     }
@@ -287,8 +298,9 @@ __device__ __noinline__ void exact_scores(const Ctx& c, uint8_t* a16_tile, int t
     const uint8_t* gs = c.base + kOffQbar;
     const uint8_t* qs = c.base + kOffKbar;
     const uint8_t* ks = qs + kTileBytes;
-    const uint32_t i = tid >> 1;
-    for (uint32_t j = tid & 1; j < 64; j += 2) {
+    constexpr uint32_t kPerRow = kComputeThreads / kChunk;
+    const uint32_t i = tid / kPerRow;
+    for (uint32_t j = tid % kPerRow; j < 64; j += kPerRow) {
         float s = 0.f;
         const bool keep = rev ? (j >= i) : (j <= i);
         if (keep) {
@@ -378,11 +390,11 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         M.abort = 0;
         fence_mbar_init();
     }
-    if (w == 4) {
+    if (w == kComputeWarps) {
         tmem_alloc(smem_u32(&M.tmem_base), kTmemCols);
         tmem_relinquish();
     }
-    if (w == 5 && l == 0) {
+    if (w == kComputeWarps + 1 && l == 0) {
         for (int t = 0; t < kNumTensors; ++t)
             if (t != TGATE || P.gated)
                 tma_prefetch_desc(&maps.m[t][0]);
@@ -397,9 +409,15 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     uint32_t n_ops = 0, n_adone = 0, n_a16 = 0, n_osdone = 0, n_accfree = 0, n_s16 = 0;
     uint32_t chunk_ctr = 0;   // chunks processed by this CTA so far: stage = ctr % 2, parity slot = ctr & 1
 
-    float S[kD];              // lanes 16-31 of compute warp w: fp32 state row of channel 16w + l - 16
-    const bool owner = (w < 4) && (l >= 16);
-    const int my_c = 16 * (w & 3) + (l & 15);
+    // State ownership: lanes 16-31 of compute warp w hold, in fp32, columns [kSc*ch, kSc*ch+kSc) of
+    // state row (channel) my_c = 16*(w&3) + (l&15), ch = w>>2.
+    constexpr int kSc = kD / kColSplit;       // O / state columns per thread
+    constexpr int kAc = 32 / kColSplit;       // score columns per thread (per 32-column half)
+    float S[kSc];
+    const bool owner = (w < kComputeWarps) && (l >= 16);
+    const int quad = w & 3, ch = (w >> 2) % kColSplit;
+    const int my_c = 16 * quad + (l & 15);
+    const int col0 = kSc * ch;                // first O / state column of this thread
 
     while (true) {
         if (tid == 0) M.item = static_cast<int>(atomicAdd(P.ctrl, 1u));
@@ -409,7 +427,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         const ItemInfo it = decode_item(P, item);
         const int npass = it.state_pass ? 2 : 1;
 
-        if (w == 4) {
+        if (w == kComputeWarps) {
             // ------------------------------------------------------------ TMA producer
             if (l == 0) {
                 uint32_t ctr = chunk_ctr;
@@ -436,7 +454,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                 }
             }
             __syncwarp();
-        } else if (w == 5) {
+        } else if (w == kComputeWarps + 1) {
             // ------------------------------------------------------------ MMA issue
             if (l == 0) {
                 constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 32);
@@ -493,19 +511,19 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             __syncwarp();
         } else {
             // ------------------------------------------------------------ compute warps
-            const size_t srow = (static_cast<size_t>(it.seq) * kD + my_c) * kD;   // row of a [B,H,K,V] state
+            const size_t srow = (static_cast<size_t>(it.seq) * kD + my_c) * kD + col0;   // this thread's part of a state row
             const size_t slot = static_cast<size_t>(it.seq) * P.NS + it.seg;
-            const uint32_t rho = 16 * w + (l & 15);   // O row (lanes 0-15) or state row (lanes 16-31)
+            const uint32_t rho = 16 * quad + (l & 15);   // O row (lanes 0-15) or state row (lanes 16-31)
             uint32_t ctr = chunk_ctr;
             float gsum = 0.f;       // log2 of the segment's total decay for channel my_c
 
             auto load_initial = [&]() {
 #pragma unroll
-                for (int x = 0; x < kD; ++x) S[x] = 0.f;
+                for (int x = 0; x < kSc; ++x) S[x] = 0.f;
                 if (owner && P.s0 != nullptr) {
                     const float4* src = reinterpret_cast<const float4*>(P.s0 + srow);
 #pragma unroll
-                    for (int x = 0; x < kD / 4; ++x) {
+                    for (int x = 0; x < kSc / 4; ++x) {
                         const float4 v4 = __ldg(src + x);
                         S[4 * x] = v4.x; S[4 * x + 1] = v4.y; S[4 * x + 2] = v4.z; S[4 * x + 3] = v4.w;
                     }
@@ -515,7 +533,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                 if (owner) {
                     float4* dst = reinterpret_cast<float4*>(dst_row);
 #pragma unroll
-                    for (int x4 = 0; x4 < kD / 4; ++x4)
+                    for (int x4 = 0; x4 < kSc / 4; ++x4)
                         dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
                 }
                 __threadfence();
@@ -530,14 +548,14 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     if (it.seg == 0) load_initial();
                     else {
 #pragma unroll
-                        for (int x = 0; x < kD; ++x) S[x] = 0.f;
+                        for (int x = 0; x < kSc; ++x) S[x] = 0.f;
                     }
                 } else {
                     if (it.seg == 0) load_initial();
                     else {
                         // decoupled look-back: S <- state entering this segment
 #pragma unroll
-                        for (int x = 0; x < kD; ++x) S[x] = 0.f;
+                        for (int x = 0; x < kSc; ++x) S[x] = 0.f;
                         float dlog = 0.f;
                         int j = it.seg - 1;
                         const uint64_t t0 = globaltimer_ns();
@@ -558,12 +576,12 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             const bool inclusive = __all_sync(0xffffffffu, f == 2u);
                             if (gave_up) break;   // result undefined, status word set
                             const float dacc = ex2(dlog);
-                            const float* src_row = inclusive ? P.incl + sj * (kD * kD) + my_c * kD
-                                                             : P.agg + sj * kAggStride + my_c * kD;
+                            const float* src_row = inclusive ? P.incl + sj * (kD * kD) + my_c * kD + col0
+                                                             : P.agg + sj * kAggStride + my_c * kD + col0;
                             if (owner) {
                                 const float4* src = reinterpret_cast<const float4*>(src_row);
 #pragma unroll
-                                for (int x4 = 0; x4 < kD / 4; ++x4) {
+                                for (int x4 = 0; x4 < kSc / 4; ++x4) {
                                     const float4 v4 = __ldcg(src + x4);
                                     S[4 * x4] = fmaf(dacc, v4.x, S[4 * x4]);
                                     S[4 * x4 + 1] = fmaf(dacc, v4.y, S[4 * x4 + 1]);
@@ -580,10 +598,10 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             // inclusive state after this segment = decay * incoming + increment
                             if (owner) {
                                 const float dseg = ex2(gsum);
-                                const float4* inc = reinterpret_cast<const float4*>(P.agg + slot * kAggStride + my_c * kD);
-                                float4* dst = reinterpret_cast<float4*>(P.incl + slot * (kD * kD) + my_c * kD);
+                                const float4* inc = reinterpret_cast<const float4*>(P.agg + slot * kAggStride + my_c * kD + col0);
+                                float4* dst = reinterpret_cast<float4*>(P.incl + slot * (kD * kD) + my_c * kD + col0);
 #pragma unroll
-                                for (int x4 = 0; x4 < kD / 4; ++x4) {
+                                for (int x4 = 0; x4 < kSc / 4; ++x4) {
                                     const float4 a4 = __ldcg(inc + x4);
                                     dst[x4] = make_float4(fmaf(dseg, S[4 * x4], a4.x), fmaf(dseg, S[4 * x4 + 1], a4.y),
                                                           fmaf(dseg, S[4 * x4 + 2], a4.z), fmaf(dseg, S[4 * x4 + 3], a4.w));
@@ -594,7 +612,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             if (tid == 0) st_release_gpu(P.flags + slot, 2u);
                         }
                     }
-                    if (owner) store_row_f16<8>(base_ptr + kOffS16, rho, 0, S);
+                    if (owner) store_row_f16<kSc / 8>(base_ptr + kOffS16, rho, col0 >> 3, S);
                     fence_proxy_async_smem();
                     mbar_arrive(smem_u32(&M.s16_ready));
                 }
@@ -609,15 +627,15 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         mbar_wait(ctx, &M.a_done, n_adone++ & 1u);
                         tc_fence_after();
                         if (!M.wide[cc & 1]) {
-                            float x[32];
-                            tmem_row<32>(tmem, w, kTmA, x);
-                            const uint32_t j0 = (l >> 4) * 32u;   // lanes 16-31 hold key rows 32-63
+                            float x[kAc];
+                            tmem_row<kAc>(tmem, quad, kTmA + kAc * ch, x);
+                            const uint32_t j0 = (l >> 4) * 32u + kAc * ch;   // lanes 16-31 hold key rows 32-63
 #pragma unroll
-                            for (uint32_t j = 0; j < 32; ++j) {
+                            for (uint32_t j = 0; j < kAc; ++j) {
                                 const bool keep = P.rev ? (j0 + j >= rho) : (j0 + j <= rho);
                                 x[j] = keep ? x[j] : 0.f;
                             }
-                            store_row_f16<4>(stage + 2 * kTileBytes, rho, j0 >> 3, x);
+                            store_row_f16<kAc / 8>(stage + 2 * kTileBytes, rho, j0 >> 3, x);
                         } else {
                             named_bar_sync(1, kComputeThreads);
                             exact_scores(ctx, stage + 2 * kTileBytes, tid);
@@ -638,8 +656,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         // lanes 16-31: S <- 2^(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
                         mbar_wait(ctx, &M.os_done, n_osdone++ & 1u);
                         tc_fence_after();
-                        float x[kD];
-                        tmem_row<kD>(tmem, w, kTmOS, x);
+                        float x[kSc];
+                        tmem_row<kSc>(tmem, quad, kTmOS + col0, x);
                         tc_fence_before();
                         mbar_arrive(smem_u32(&M.acc_free));
                         const float b4 = M.b4s[cc & 1][my_c];
@@ -647,12 +665,12 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         const float mul = owner ? 1.f : P.scale;
                         if (owner) gsum += b4;
 #pragma unroll
-                        for (int v = 0; v < kD; ++v) {
+                        for (int v = 0; v < kSc; ++v) {
                             S[v] = fmaf(dec, S[v], x[v]);
                             x[v] = S[v] * mul;
                         }
                         if (!state_only) {
-                            store_row_f16<8>(owner ? base_ptr + kOffS16 : stage, rho, 0, x);
+                            store_row_f16<kSc / 8>(owner ? base_ptr + kOffS16 : stage, rho, col0 >> 3, x);
                             fence_proxy_async_smem();
                             if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.s16_ready));
                             named_bar_sync(1, kComputeThreads);
@@ -674,17 +692,17 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
 
                 if (state_only) {
                     if (it.seg == 0) {
-                        publish(P.incl + slot * (kD * kD) + my_c * kD, 2u);
+                        publish(P.incl + slot * (kD * kD) + my_c * kD + col0, 2u);
                     } else {
-                        if (owner) P.agg[slot * kAggStride + kD * kD + my_c] = gsum;
-                        publish(P.agg + slot * kAggStride + my_c * kD, 1u);
+                        if (owner && ch == 0) P.agg[slot * kAggStride + kD * kD + my_c] = gsum;
+                        publish(P.agg + slot * kAggStride + my_c * kD + col0, 1u);
                     }
                 }
             }
             if (it.seg == P.NS - 1 && P.sT != nullptr && owner) {
                 float4* dst = reinterpret_cast<float4*>(P.sT + srow);
 #pragma unroll
-                for (int x4 = 0; x4 < kD / 4; ++x4)
+                for (int x4 = 0; x4 < kSc / 4; ++x4)
                     dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
             }
         }
@@ -695,7 +713,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     if (tid == 0) tma_store_wait_all();
     tc_fence_before();
     __syncthreads();
-    if (w == 4) tmem_dealloc(tmem, kTmemCols);
+    if (w == kComputeWarps) tmem_dealloc(tmem, kTmemCols);
 }
 
 }  // namespace gla
