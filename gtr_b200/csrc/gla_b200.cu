@@ -4,6 +4,7 @@
 #include "gla_b200.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -250,7 +251,9 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     if (a->direction >= 2 && (a->grid_h <= 0 || a->grid_w <= 0)) return GLA_B200_ERR_SHAPE;
     if (a->scale != a->scale || a->gk_normalizer < 0.f) return GLA_B200_ERR_ARG;
     const bool gated = a->out_gate != nullptr || a->rms_weight != nullptr;
+#ifndef GLA_TRACE
     if (gated) return GLA_B200_ERR_ARG;   // fused epilogue: not in this build of the kernel yet
+#endif
     if (static_cast<int64_t>(a->B) * a->T * a->H == 0) return GLA_B200_OK;   // nothing to do
     if (!a->q || !a->k || !a->v || !a->g || !a->o) return GLA_B200_ERR_NULL;
     if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->g) || !aligned16(a->o) ||
@@ -288,7 +291,11 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     // segmentation
     const int NT = num_chunks(a->T);
     const int nseq = a->B * a->H;
-    const int slots = 2 * di.sms;
+    int slots = 2 * di.sms;
+    if (const char* e = getenv("GLA_B200_MAX_CTAS")) {   // tuning aid: cap the persistent grid
+        const int cap = atoi(e);
+        if (cap > 0 && cap < slots) slots = cap;
+    }
     int cps;
     if (a->segments > 0) cps = a->segments;
     else if (nseq >= slots) cps = NT;
@@ -328,6 +335,10 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     P.agg = reinterpret_cast<float*>(ws + L.agg);
     P.incl = reinterpret_cast<float*>(ws + L.incl);
     P.wait_limit_us = a->wait_limit ? a->wait_limit : 2000000u;
+#ifdef GLA_TRACE
+    P.trace = static_cast<unsigned long long*>(const_cast<void*>(a->rms_weight));
+    P.dbg = getenv("GLA_DBG") ? atoi(getenv("GLA_DBG")) : 0;   // debug builds smuggle the trace buffer here
+#endif
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     ce = cudaMemsetAsync(ws, 0, L.clear_bytes, stream);

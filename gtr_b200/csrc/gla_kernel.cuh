@@ -77,7 +77,19 @@ struct Params {
     float* agg;          // per (sequence, segment): 4096 state increment + 64 log2 decay
     float* incl;         // per (sequence, segment): 4096 state after the segment
     uint32_t wait_limit_us;
+#ifdef GLA_TRACE
+    unsigned long long* trace;   // debug builds only: (event, time) pairs of CTA 0
+    int dbg;                     // debug builds only: ablation switches (results become wrong)
+#endif
 };
+
+#ifdef GLA_TRACE
+// debug builds: lane 0 of every warp of CTA 0 appends (clock << 8 | event) to its own region, no atomics
+#define GLA_EV(id) do { if (blockIdx.x == 0 && !(P.dbg & 128) && (threadIdx.x & 31) == 0 && trace_n < 4096u) { \
+        P.trace[(threadIdx.x >> 5) * 4096u + trace_n++] = ((unsigned long long)clock64() << 8) | (unsigned long long)(id); } } while (0)
+#else
+#define GLA_EV(id) do { } while (0)
+#endif
 
 constexpr int kAggStride = kD * kD + kD;
 
@@ -111,7 +123,16 @@ struct Ctx {
     uint8_t* base;       // generic pointer to the 1024-aligned shared-memory base
     uint32_t smem;       // the same as a shared-window address
     uint64_t deadline_span_ns;
+#ifdef GLA_TRACE
+    uint32_t* trace_n;
+#endif
 };
+#ifdef GLA_TRACE
+#define GLA_EVC(c, id) do { if (blockIdx.x == 0 && !((c).p->dbg & 128) && (threadIdx.x & 31) == 0 && *(c).trace_n < 4096u) { \
+        (c).p->trace[(threadIdx.x >> 5) * 4096u + (*(c).trace_n)++] = ((unsigned long long)clock64() << 8) | (unsigned long long)(id); } } while (0)
+#else
+#define GLA_EVC(c, id) do { } while (0)
+#endif
 
 __device__ __forceinline__ void raise_timeout(const Ctx& c, uint32_t where) {
     c.misc->abort = 1;
@@ -164,9 +185,11 @@ __device__ __forceinline__ void for_each_box(int p0, int L, int Hc, int rev, F f
 
 __device__ __forceinline__ int chunk_valid(int p0, int L) { return min(kChunk, L - p0); }
 
-__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
-__device__ __forceinline__ void sts32(uint8_t* p, uint32_t v) { *reinterpret_cast<uint32_t*>(p) = v; }
-__device__ __forceinline__ void sts64(uint8_t* p, float x, float y) { *reinterpret_cast<float2*>(p) = make_float2(x, y); }
+// Shared memory is always addressed through the shared window (ld.shared / st.shared): generic
+// loads of shared data take the slow path through L1TEX.
+__device__ __forceinline__ uint32_t lds32(uint32_t a) { return ld_shared_u32(a); }
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) { st_shared_u32(a, v); }
+__device__ __forceinline__ void sts64(uint32_t a, float x, float y) { st_shared_f2(a, x, y); }
 
 // ------------------------------------------------------------------------------------------
 // Raw-logit gates (gk_normalizer > 0): rewrite the gate tile in place as fp16 log gates,
@@ -180,12 +203,17 @@ __device__ __noinline__ void logits_to_log_gates(uint8_t* tg, float inv_norm, in
     }
 }
 
+#ifdef GLA_TRACE
+#define GLA_DBG(bit) ((c.p->dbg >> (bit)) & 1)
+#else
+#define GLA_DBG(bit) 0
+#endif
 // Gate math for one chunk (all compute threads).  Thread (w, l) owns logical rows
 // 8w..8w+7 and channels 2l, 2l+1.  Logical row = position inside the chunk along the scan;
 // the physical (shared-memory / TMEM) row is mirrored for reversed scans.  Tiles are rows of
 // 128 bytes whose 16-byte units are XOR-swizzled with (row & 7); since 8w is a multiple of 8
 // the swizzle of logical row i depends on i only, which is a compile-time constant here.
-__device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, int valid, int w, int l,
+__device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, int n, int valid, int w, int l,
                                           bool state_only) {
     constexpr int R = kRowsPerThread;
     static_assert(R == 8, "the swizzle shortcut below needs 8 rows per thread");
@@ -201,18 +229,16 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, i
     // tf32 tiles: channel 2l lives in half (l >> 4), 16-byte unit (l & 15) >> 1, byte (l & 1) * 8
     const uint32_t ly = rev ? (((l & 15u) >> 1) ^ 7u) : ((l & 15u) >> 1);
     const uint32_t lb32 = (l >> 4) * kTileBytes + ((l & 1u) << 3);
-    uint8_t* tq = stage;
-    uint8_t* tk = stage + kTileBytes;
-    uint8_t* tg = stage + 2 * kTileBytes;
-    uint8_t* tv = stage + 3 * kTileBytes;
-    uint8_t* qbar = c.base + kOffQbar;
-    uint8_t* kbar = c.base + kOffKbar;
+    const uint32_t tq = stage, tk = stage + kTileBytes, tg = stage + 2 * kTileBytes, tv = stage + 3 * kTileBytes;
+    const uint32_t qbar = c.smem + kOffQbar, kbar = c.smem + kOffKbar;
     const uint32_t c0 = 2u * l;
+    const uint32_t tot_sa = smem_u32(&M.tot[par][0][c0]);   // + ww * kD * 4
 #define GLA_OFF16(i) (row0 + (i) * step + static_cast<int>(((lx ^ static_cast<uint32_t>(i)) << 4) + lb))
 #define GLA_OFF32(i) (row0 + (i) * step + static_cast<int>(((ly ^ static_cast<uint32_t>(i)) << 4) + lb32))
 
+    GLA_EVC(c, 45);
     if (P.inv_norm > 0.f) {
-        logits_to_log_gates(tg, P.inv_norm, 32 * w + l);
+        logits_to_log_gates(c.base + (tg - c.smem), P.inv_norm, 32 * w + l);
         named_bar_sync(1, kComputeThreads);
     }
     uint32_t graw[R], kraw[R], qraw[R];
@@ -223,6 +249,8 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, i
         kraw[i] = lds32(tk + GLA_OFF16(i));
         qraw[i] = state_only ? 0u : lds32(tq + GLA_OFF16(i));
     }
+    GLA_EVC(c, 44);
+    if (GLA_DBG(0)) { fence_proxy_async_smem(); return; }
     float cs0[R], cs1[R];
     {
         float a0 = 0.f, a1 = 0.f;
@@ -235,19 +263,21 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, i
             cs0[i] = a0;
             cs1[i] = a1;
         }
-        *reinterpret_cast<float2*>(&M.tot[par][w][c0]) = make_float2(a0, a1);
+        sts64(tot_sa + w * kD * 4, a0, a1);
     }
+    GLA_EVC(c, 40);
     named_bar_sync(1, kComputeThreads);
+    GLA_EVC(c, 41);
     float off0 = 0.f, off1 = 0.f, b40 = 0.f, b41 = 0.f, gm0 = 0.f, gm1 = 0.f;
 #pragma unroll
     for (int ww = 0; ww < kComputeWarps; ++ww) {
-        const float2 t = *reinterpret_cast<const float2*>(&M.tot[par][ww][c0]);
+        const float2 t = ld_shared_f2(tot_sa + ww * kD * 4);
         if (ww < w) { off0 += t.x; off1 += t.y; }
         if (ww < kComputeWarps / 2) { gm0 += t.x; gm1 += t.y; }
         b40 += t.x;
         b41 += t.y;
     }
-    if (w == 0) *reinterpret_cast<float2*>(&M.b4s[par][c0]) = make_float2(b40, b41);
+    if (w == 0) sts64(smem_u32(&M.b4s[par][c0]), b40, b41);
     bool wide = false;
     float e10 = 0.f, e11 = 0.f, e20 = 0.f, e21 = 0.f;
     if (!state_only) {
@@ -258,6 +288,7 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, i
         e20 = ex2(gm0 - b40);
         e21 = ex2(gm1 - b41);
     }
+    if (GLA_DBG(2)) { fence_proxy_async_smem(); return; }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const bool live = R * w + i < valid;
@@ -271,7 +302,8 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, i
             const float2 qv = unpack_half2(qr);
             const float qh0 = qv.x * ex2(G0), qh1 = qv.y * ex2(G1);
             sts32(tq + GLA_OFF16(i), pack_half2_sat(qh0, qh1));
-            if (!wide) {
+            if (GLA_DBG(1)) {
+            } else if (!wide) {
                 sts64(qbar + GLA_OFF32(i), round_tf32(qh0 * e10), round_tf32(qh1 * e11));
                 sts64(kbar + GLA_OFF32(i), round_tf32(kh0 * e20), round_tf32(kh1 * e21));
             } else {  // exact path operands, plain layouts: G fp32 [64][64]; raw q, k fp16 [64][64]
@@ -284,7 +316,9 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint8_t* stage, int n, i
     }
 #undef GLA_OFF16
 #undef GLA_OFF32
+    GLA_EVC(c, 42);
     fence_proxy_async_smem();
+    GLA_EVC(c, 43);
 }
 
 __device__ __forceinline__ uint32_t sw_f16(uint32_t row, uint32_t col) {     // col in fp16 elements
@@ -307,8 +341,8 @@ __device__ __noinline__ void exact_scores(const Ctx& c, uint8_t* a16_tile, int t
             for (uint32_t ch = 0; ch < 64; ch += 2) {
                 const float2 gi = *reinterpret_cast<const float2*>(gs + i * 256u + ch * 4u);
                 const float2 gj = *reinterpret_cast<const float2*>(gs + j * 256u + ch * 4u);
-                const float2 qv = unpack_half2(lds32(qs + i * 128u + ch * 2u));
-                const float2 kv = unpack_half2(lds32(ks + j * 128u + ch * 2u));
+                const float2 qv = unpack_half2(*reinterpret_cast<const uint32_t*>(qs + i * 128u + ch * 2u));
+                const float2 kv = unpack_half2(*reinterpret_cast<const uint32_t*>(ks + j * 128u + ch * 2u));
                 s += qv.x * kv.x * ex2(gi.x - gj.x);
                 s += qv.y * kv.y * ex2(gi.y - gj.y);
             }
@@ -331,13 +365,12 @@ __device__ __forceinline__ void tmem_row(uint32_t tmem_base, int w, uint32_t col
 
 // Write 8*N8 floats as fp16 into 16-byte units unit0.. of one row of a swizzled tile.
 template <int N8>
-__device__ __forceinline__ void store_row_f16(uint8_t* tile, uint32_t row, uint32_t unit0, const float* x) {
+__device__ __forceinline__ void store_row_f16(uint32_t tile, uint32_t row, uint32_t unit0, const float* x) {
 #pragma unroll
     for (uint32_t m = 0; m < N8; ++m) {
-        uint8_t* a = tile + row * 128u + ((((unit0 + m) ^ row) & 7u) << 4);
-        *reinterpret_cast<uint4*>(a) =
-            make_uint4(pack_half2_sat(x[8 * m], x[8 * m + 1]), pack_half2_sat(x[8 * m + 2], x[8 * m + 3]),
-                       pack_half2_sat(x[8 * m + 4], x[8 * m + 5]), pack_half2_sat(x[8 * m + 6], x[8 * m + 7]));
+        const uint32_t a = tile + row * 128u + ((((unit0 + m) ^ row) & 7u) << 4);
+        st_shared_v4(a, pack_half2_sat(x[8 * m], x[8 * m + 1]), pack_half2_sat(x[8 * m + 2], x[8 * m + 3]),
+                     pack_half2_sat(x[8 * m + 4], x[8 * m + 5]), pack_half2_sat(x[8 * m + 6], x[8 * m + 7]));
     }
 }
 
@@ -368,6 +401,9 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
 
     const int tid = threadIdx.x;
     const int w = tid >> 5, l = tid & 31;
+#ifdef GLA_TRACE
+    uint32_t trace_n = 0;
+#endif
 
     Ctx ctx;
     ctx.p = &P;
@@ -375,6 +411,9 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     ctx.base = base_ptr;
     ctx.smem = base;
     ctx.deadline_span_ns = static_cast<uint64_t>(P.wait_limit_us) * 1000ull;
+#ifdef GLA_TRACE
+    ctx.trace_n = &trace_n;
+#endif
 
     if (tid == 0) {
         for (int s = 0; s < kNumStages; ++s) {
@@ -436,6 +475,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     for (int i = 0; i < it.nchunks; ++i, ++ctr) {
                         const uint32_t s = ctr % kNumStages;
                         mbar_wait(ctx, &M.empty[s], (n_empty[s]++ & 1u) ^ 1u);
+                        GLA_EV(30);
                         const int p0 = (it.first_chunk + i) * kChunk;
                         const int valid = chunk_valid(p0, P.T);
                         const int ntens = state_only ? 3 : 4;
@@ -471,6 +511,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                                        tv = stage + 3 * kTileBytes;
                         mbar_wait(ctx, &M.full[s], n_full[s]++ & 1u);
                         mbar_wait(ctx, &M.ops_ready, n_ops++ & 1u);
+                        GLA_EV(20);
                         tc_fence_after();
                         if (!state_only) {
                             if (!M.wide[ctr & 1]) {
@@ -483,10 +524,12 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                                 }
                             }
                             umma_commit(smem_u32(&M.a_done));
+                            GLA_EV(21);
                             mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
                         }
                         // both accumulators of the O/S columns must have been read by the epilogue
                         mbar_wait(ctx, &M.acc_free, (n_accfree++ & 1u) ^ 1u);
+                        GLA_EV(22);
                         tc_fence_after();
                         if (!state_only) {
 #pragma unroll
@@ -494,6 +537,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                                 umma_f16(tmO, umma_desc_sw128(tq + ks * 32u),
                                          umma_desc_sw128(base + kOffS16 + ks * 2048u, 8192), idO, ks);
                             mbar_wait(ctx, &M.a16_ready, n_a16++ & 1u);
+                            GLA_EV(23);
                             tc_fence_after();
 #pragma unroll
                             for (uint32_t ks = 0; ks < 4; ++ks)
@@ -505,6 +549,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             umma_f16(tmS, umma_desc_sw128(tk + ks * 2048u, 8192),
                                      umma_desc_sw128(tv + ks * 2048u, 8192), idS, ks);
                         umma_commit(smem_u32(&M.os_done));
+                        GLA_EV(24);
                     }
                 }
             }
@@ -612,7 +657,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             if (tid == 0) st_release_gpu(P.flags + slot, 2u);
                         }
                     }
-                    if (owner) store_row_f16<kSc / 8>(base_ptr + kOffS16, rho, col0 >> 3, S);
+                    if (owner) store_row_f16<kSc / 8>(base + kOffS16, rho, col0 >> 3, S);
                     fence_proxy_async_smem();
                     mbar_arrive(smem_u32(&M.s16_ready));
                 }
@@ -621,10 +666,11 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                 for (int i = -1; i < it.nchunks; ++i) {
                     const uint32_t cc = ctr + static_cast<uint32_t>(i);       // running index of chunk i
                     const uint32_t s = cc % kNumStages;
-                    uint8_t* stage = base_ptr + kOffStage + s * kStageBytes;
+                    const uint32_t stage = base + kOffStage + s * kStageBytes;
                     if (i >= 0 && !state_only) {
                         // scores: TMEM -> causal mask -> fp16 tile (takes the place of the raw gate tile)
                         mbar_wait(ctx, &M.a_done, n_adone++ & 1u);
+                        GLA_EV(10);
                         tc_fence_after();
                         if (!M.wide[cc & 1]) {
                             float x[kAc];
@@ -638,29 +684,33 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             store_row_f16<kAc / 8>(stage + 2 * kTileBytes, rho, j0 >> 3, x);
                         } else {
                             named_bar_sync(1, kComputeThreads);
-                            exact_scores(ctx, stage + 2 * kTileBytes, tid);
+                            exact_scores(ctx, base_ptr + kOffStage + s * kStageBytes + 2 * kTileBytes, tid);
                         }
                         fence_proxy_async_smem();
                         tc_fence_before();
                         mbar_arrive(smem_u32(&M.a16_ready));
+                        GLA_EV(11);
                     }
                     if (i + 1 < it.nchunks) {
                         const uint32_t s1 = (cc + 1) % kNumStages;
                         mbar_wait(ctx, &M.full[s1], n_full[s1]++ & 1u);
-                        gate_math(ctx, base_ptr + kOffStage + s1 * kStageBytes, static_cast<int>(cc + 1),
+                        GLA_EV(12);
+                        gate_math(ctx, base + kOffStage + s1 * kStageBytes, static_cast<int>(cc + 1),
                                   chunk_valid((it.first_chunk + i + 1) * kChunk, P.T), w, l, state_only);
                         if (!state_only) mbar_arrive(smem_u32(&M.ops_ready));
+                        GLA_EV(13);
                     }
                     if (i >= 0) {
                         // lanes 0-15: outputs -> scale -> fp16 tile (takes the place of qh) -> TMA store
                         // lanes 16-31: S <- 2^(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
                         mbar_wait(ctx, &M.os_done, n_osdone++ & 1u);
+                        GLA_EV(14);
                         tc_fence_after();
                         float x[kSc];
                         tmem_row<kSc>(tmem, quad, kTmOS + col0, x);
                         tc_fence_before();
                         mbar_arrive(smem_u32(&M.acc_free));
-                        const float b4 = M.b4s[cc & 1][my_c];
+                        const float b4 = ld_shared_f(smem_u32(&M.b4s[cc & 1][my_c]));
                         const float dec = owner ? ex2(b4) : 0.f;
                         const float mul = owner ? 1.f : P.scale;
                         if (owner) gsum += b4;
@@ -670,21 +720,22 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             x[v] = S[v] * mul;
                         }
                         if (!state_only) {
-                            store_row_f16<kSc / 8>(owner ? base_ptr + kOffS16 : stage, rho, col0 >> 3, x);
+                            store_row_f16<kSc / 8>(owner ? base + kOffS16 : stage, rho, col0 >> 3, x);
                             fence_proxy_async_smem();
                             if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.s16_ready));
+                            GLA_EV(15);
                             named_bar_sync(1, kComputeThreads);
                             if (tid == 0) {
                                 const int p0 = (it.first_chunk + i) * kChunk;
-                                const uint32_t st = base + kOffStage + s * kStageBytes;
                                 for_each_box(p0, P.T, P.Hc, P.rev, [&](int id, int r, int c, int row) {
-                                    tma_store_5d(&maps.m[TO][id], st + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
+                                    tma_store_5d(&maps.m[TO][id], stage + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
                                 });
                                 tma_store_commit();
                                 tma_store_wait_read();
                             }
                         }
                         if (tid == 0) mbar_arrive(smem_u32(&M.empty[s]));
+                        GLA_EV(16);
                     }
                     if (state_only && i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.ops_ready));
                 }
