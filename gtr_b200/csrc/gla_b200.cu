@@ -300,10 +300,11 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     if (a->segments > 0) cps = a->segments;
     else if (nseq >= slots) cps = NT;
     else {
-        const long total = static_cast<long>(NT) * nseq;
-        cps = static_cast<int>(total / (3L * slots));
+        // aim for slightly more work items than CTA slots: few, long segments keep the share of the
+        // state-only pre-pass and of the look-back small
+        const int per_seq = (slots + nseq - 1) / nseq;          // segments per sequence for one full wave
+        cps = (NT + per_seq - 1) / per_seq;
         if (cps < kMinAutoCps) cps = kMinAutoCps;
-        if (cps > 32) cps = 32;
     }
     if (cps > NT) cps = NT;
     const int NS = (NT + cps - 1) / cps;

@@ -21,6 +21,9 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 
 // ------------------------------------------------------------------ mbarrier
+// Upper bound, in ns, for one try_wait to stay suspended in hardware before it reports "not yet";
+// the caller's bounded loop re-arms it, so waiting warps issue very few instructions.
+constexpr uint32_t kTryWaitHintNs = 20000;
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -34,10 +37,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kTryWaitHintNs)
         : "memory");
     return ok != 0;
 }

@@ -500,6 +500,9 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                 constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 32);
                 constexpr uint32_t idO = umma_idesc(FMT_F16, 0, 1, 64, 64);
                 constexpr uint32_t idS = umma_idesc(FMT_F16, 1, 1, 64, 64);
+                // descriptors differ only in their 14-bit start-address field: add byte offsets >> 4
+                const uint64_t dQbar = umma_desc_sw128(base + kOffQbar), dKbar = umma_desc_sw128(base + kOffKbar);
+                const uint64_t dS16 = umma_desc_sw128(base + kOffS16, 8192);
                 const uint32_t tmA = tmem + kTmA, tmO = tmem + kTmOS, tmS = tmem + kTmOS + kLane16;
                 uint32_t ctr = chunk_ctr;
                 for (int pass = 0; pass < npass; ++pass) {
@@ -507,8 +510,9 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     for (int i = 0; i < it.nchunks; ++i, ++ctr) {
                         const uint32_t s = ctr % kNumStages;
                         const uint32_t stage = base + kOffStage + s * kStageBytes;
-                        const uint32_t tq = stage, tk = stage + kTileBytes, ta16 = stage + 2 * kTileBytes,
-                                       tv = stage + 3 * kTileBytes;
+                        const uint64_t dq = umma_desc_sw128(stage), dk = umma_desc_sw128(stage + kTileBytes, 8192),
+                                       da16 = umma_desc_sw128(stage + 2 * kTileBytes),
+                                       dv = umma_desc_sw128(stage + 3 * kTileBytes, 8192);
                         mbar_wait(ctx, &M.full[s], n_full[s]++ & 1u);
                         mbar_wait(ctx, &M.ops_ready, n_ops++ & 1u);
                         GLA_EV(20);
@@ -517,10 +521,9 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             if (!M.wide[ctr & 1]) {
 #pragma unroll
                                 for (uint32_t ks = 0; ks < 8; ++ks) {
-                                    const uint32_t o = (ks >> 2) * kTileBytes + (ks & 3) * 32u;
-                                    const uint64_t da = umma_desc_sw128(base + kOffQbar + o);
-                                    umma_tf32(tmA, da, umma_desc_sw128(base + kOffKbar + o), idA, ks);
-                                    umma_tf32(tmA + kLane16, da, umma_desc_sw128(base + kOffKbar + o + 32 * 128), idA, ks);
+                                    const uint32_t o = ((ks >> 2) * kTileBytes + (ks & 3) * 32u) >> 4;
+                                    umma_tf32(tmA, dQbar + o, dKbar + o, idA, ks);
+                                    umma_tf32(tmA + kLane16, dQbar + o, dKbar + o + ((32 * 128) >> 4), idA, ks);
                                 }
                             }
                             umma_commit(smem_u32(&M.a_done));
@@ -534,20 +537,17 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         if (!state_only) {
 #pragma unroll
                             for (uint32_t ks = 0; ks < 4; ++ks)
-                                umma_f16(tmO, umma_desc_sw128(tq + ks * 32u),
-                                         umma_desc_sw128(base + kOffS16 + ks * 2048u, 8192), idO, ks);
+                                umma_f16(tmO, dq + ks * 2u, dS16 + ks * 128u, idO, ks);
                             mbar_wait(ctx, &M.a16_ready, n_a16++ & 1u);
                             GLA_EV(23);
                             tc_fence_after();
 #pragma unroll
                             for (uint32_t ks = 0; ks < 4; ++ks)
-                                umma_f16(tmO, umma_desc_sw128(ta16 + ks * 32u),
-                                         umma_desc_sw128(tv + ks * 2048u, 8192), idO, 1);
+                                umma_f16(tmO, da16 + ks * 2u, dv + ks * 128u, idO, 1);
                         }
 #pragma unroll
                         for (uint32_t ks = 0; ks < 4; ++ks)
-                            umma_f16(tmS, umma_desc_sw128(tk + ks * 2048u, 8192),
-                                     umma_desc_sw128(tv + ks * 2048u, 8192), idS, ks);
+                            umma_f16(tmS, dk + ks * 128u, dv + ks * 128u, idS, ks);
                         umma_commit(smem_u32(&M.os_done));
                         GLA_EV(24);
                     }
