@@ -207,11 +207,18 @@ def run_ours(args, rank, local_rank, world):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident timing: CUDA events around every launch on the launching stream
-    for i in range(max(args.warmup, 3)):
-        step(i, dev_sets[i % n_sets])
-    barrier()
+    # ---- device-resident timing: CUDA events around every launch on the launching stream.
+    # The clock sampler runs from the warm-up on (at least `warmup` steps and one second under
+    # load, so that clocks have ramped) through the timed region.
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    t_w = time.perf_counter()
+    i = 0
+    while i < max(args.warmup, 3) or time.perf_counter() - t_w < 1.0:
+        step(i, dev_sets[i % n_sets])
+        i += 1
+        if i % 64 == 0:
+            torch.cuda.synchronize()
+    barrier()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     t_all0, t_all1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -293,7 +300,7 @@ def run_ours(args, rank, local_rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))

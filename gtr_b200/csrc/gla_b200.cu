@@ -250,9 +250,13 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     if (gh < 0 || gw < 0 || static_cast<int64_t>(gh) * gw != a->T) return GLA_B200_ERR_SHAPE;
     if (a->direction >= 2 && (a->grid_h <= 0 || a->grid_w <= 0)) return GLA_B200_ERR_SHAPE;
     if (a->scale != a->scale || a->gk_normalizer < 0.f) return GLA_B200_ERR_ARG;
+#ifdef GLA_TRACE
+    const bool gated = false;             // debug builds carry the trace buffer in rms_weight
+#else
     const bool gated = a->out_gate != nullptr || a->rms_weight != nullptr;
-#ifndef GLA_TRACE
-    if (gated) return GLA_B200_ERR_ARG;   // fused epilogue: not in this build of the kernel yet
+    if (gated && (!a->out_gate || !a->rms_weight)) return GLA_B200_ERR_NULL;
+    if (gated && (!aligned16(a->out_gate) || !aligned16(a->rms_weight))) return GLA_B200_ERR_ALIGN;
+    if (gated && !(a->rms_eps >= 0.f)) return GLA_B200_ERR_ARG;
 #endif
     if (static_cast<int64_t>(a->B) * a->T * a->H == 0) return GLA_B200_OK;   // nothing to do
     if (!a->q || !a->k || !a->v || !a->g || !a->o) return GLA_B200_ERR_NULL;
@@ -324,11 +328,18 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     P.rev = a->direction & 1;
     P.NS = NS; P.cps = cps;
     P.num_items = nseq * NS;
-    P.gated = 0;
+    P.gated = gated ? 1 : 0;
     P.scale = a->scale;
     P.inv_norm = a->gk_normalizer > 0.f ? 1.f / a->gk_normalizer : 0.f;
     P.rms_eps = a->rms_eps;
-    P.rms_w = nullptr;
+    P.rms_w = gated ? static_cast<const __half*>(a->rms_weight) : nullptr;
+    P.gate = gated ? static_cast<const __half*>(a->out_gate) : nullptr;
+    if (gated) {
+        int64_t gs[3];
+        rc = resolve_strides(a->gate_stride, a->T, a->H, gla::kD, gs);
+        if (rc != GLA_B200_OK) return rc;
+        P.gate_sb = gs[0]; P.gate_st = gs[1]; P.gate_sh = gs[2];
+    }
     P.s0 = a->initial_state;
     P.sT = a->final_state;
     P.ctrl = reinterpret_cast<uint32_t*>(ws + L.ctrl);

@@ -69,7 +69,9 @@ struct Params {
     float scale;
     float inv_norm;      // 1/gk_normalizer, or 0 when g already is a log gate
     float rms_eps;
-    const __half* rms_w;
+    const __half* rms_w;      // [64]
+    const __half* gate;       // output gate [B,T,H,64] with element strides gate_sb/st/sh
+    long long gate_sb, gate_st, gate_sh;
     const float* s0;
     float* sT;
     uint32_t* ctrl;      // [0] ticket, [1] status
@@ -112,6 +114,7 @@ struct Misc {
     uint32_t wide[2];
     alignas(16) float tot[2][kComputeWarps][kD];   // per-warp gate sums of the two chunks in flight (float2 access)
     alignas(16) float b4s[2][kD];      // chunk totals G_L per channel
+    float ssq[kColSplit][kChunk];      // fused epilogue: per-row partial sums of squares
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "misc block too large");
 
@@ -718,6 +721,42 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         for (int v = 0; v < kSc; ++v) {
                             S[v] = fmaf(dec, S[v], x[v]);
                             x[v] = S[v] * mul;
+                        }
+                        if (!state_only && P.gated) {
+                            // y = o * rsqrt(mean(o^2) + eps) * w * silu(gate); a row's 64 columns are split over
+                            // kColSplit warps, which exchange their partial sums of squares through shared memory
+                            float ss = 0.f;
+#pragma unroll
+                            for (int v = 0; v < kSc; ++v) ss = fmaf(x[v], x[v], ss);
+                            if (!owner) M.ssq[ch][rho] = ss;
+                            named_bar_sync(1, kComputeThreads);
+                            if (!owner) {
+                                float tot = 0.f;
+#pragma unroll
+                                for (int cc2 = 0; cc2 < kColSplit; ++cc2) tot += M.ssq[cc2][rho];
+                                const float rinv = rsqrtf(tot * (1.f / kD) + P.rms_eps);
+                                // token read at this row of the chunk (same mapping as the TMA boxes)
+                                const int p0 = (it.first_chunk + i) * kChunk;
+                                const int u = (P.rev ? (P.T - p0 - kChunk) : p0) + static_cast<int>(rho);
+                                if (u >= 0 && u < P.T) {
+                                    const int cc3 = u / P.Hc, rr = u - cc3 * P.Hc;
+                                    const long long tok = (P.Wc > 1) ? static_cast<long long>(rr) * P.Wc + cc3 : u;
+                                    const uint4* gp = reinterpret_cast<const uint4*>(
+                                        P.gate + it.b * P.gate_sb + tok * P.gate_st + it.h * P.gate_sh + col0);
+                                    const uint4* wp = reinterpret_cast<const uint4*>(P.rms_w + col0);
+#pragma unroll
+                                    for (int v8 = 0; v8 < kSc / 8; ++v8) {
+                                        const uint4 g4 = __ldg(gp + v8), w4 = __ldg(wp + v8);
+                                        const uint32_t gu[4] = {g4.x, g4.y, g4.z, g4.w}, wu[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                                        for (int q2 = 0; q2 < 4; ++q2) {
+                                            const float2 gf = unpack_half2(gu[q2]), wf = unpack_half2(wu[q2]);
+                                            x[8 * v8 + 2 * q2] *= rinv * wf.x * (gf.x / (1.f + __expf(-gf.x)));
+                                            x[8 * v8 + 2 * q2 + 1] *= rinv * wf.y * (gf.y / (1.f + __expf(-gf.y)));
+                                        }
+                                    }
+                                }
+                            }
                         }
                         if (!state_only) {
                             store_row_f16<kSc / 8>(owner ? base + kOffS16 : stage, rho, col0 >> 3, x);

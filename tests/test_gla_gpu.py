@@ -279,3 +279,29 @@ def test_trt_enqueue_shape(G):
     _check(ref, o.float().cpu())
     assert _lib.lib().gla_b200_trt_enqueue(ins, 5, outs, dims, 0.125, 0.0, 0.0, ws.data_ptr(),
                                            ws.numel() * 4, ctypes.c_void_p(stream)) == -1
+
+
+@pytest.mark.parametrize("direction,grid,T", [(0, None, 300), (3, (20, 23), 460), (2, (40, 40), 1600)])
+def test_fused_rmsnorm_swish_gate_epilogue(G, direction, grid, T):
+    """chunk_gla_run_gated == RMSNorm(GLA) * w * silu(gate) (reference: chunk_gla_run_gated, test_gla.py:102-119)."""
+    from oracle import c_oracle, gla_ref
+    B, H = 2, 3
+    q, k, v, g = gla_ref.make_inputs(B, T, H, seed=21 + direction)
+    gen = torch.Generator().manual_seed(5)
+    gate = torch.randn(B, T, H, 64, generator=gen).half()
+    w = (torch.randn(64, generator=gen).abs() + 0.5).half()
+    o_ref, _ = c_oracle.forward(q, k, v, g, direction=direction, grid_hw=grid)
+    y_ref = gla_ref.rmsnorm_swish_gate(o_ref, gate, w, 1e-5)
+    ws = G.make_workspace(B, T, H, "cuda")
+    y = torch.full((B, T, H, 64), float("nan"), dtype=torch.float16, device="cuda")
+    G.chunk_gla_run_gated(q.cuda(), k.cuda(), v.cuda(), g.cuda(), gate.cuda(), w.cuda(), 0.125, 1e-5, ws, y,
+                          direction=direction, grid_hw=grid)
+    G.check_status(ws)
+    m = gla_ref.error_metrics(y_ref, y.float().cpu())
+    assert m["finite"] and m["rel_l2"] <= REL_L2, m
+    # unfused: plain operator followed by the standalone kernel gives the same result to rounding
+    o = torch.empty_like(y)
+    G.chunk_gla_run(q.cuda(), k.cuda(), v.cuda(), g.cuda(), 0.125, ws, o, direction=direction, grid_hw=grid)
+    G.rmsnorm_gated(o, gate.cuda(), w.cuda(), o, 1e-5)
+    m2 = gla_ref.error_metrics(y_ref, o.float().cpu())
+    assert m2["finite"] and m2["rel_l2"] <= 2 * REL_L2, m2
