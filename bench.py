@@ -170,6 +170,59 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def backbone_flops_per_image(dim=768, depth=12, heads=12, tokens=8192, inter=3072, low_rank=16):
+    """Dense FLOPs of one image through the blocks (GEMMs, depthwise conv, GLA recurrence count)."""
+    gemm = 2 * (dim * (4 * dim + low_rank) + low_rank * dim + dim * dim + 3 * dim * inter)
+    gla = heads * (4 * 64 * 64 + 4 * 64 * 64)        # recurrence 4KV per token-head + chunk-local scores/products
+    conv = 2 * 9 * inter
+    return depth * tokens * (gemm + gla + conv)
+
+
+def run_backbone(args, rank, local_rank, world, dist):
+    """configs[3]: 12 blocks, dim 768, 12 heads of 64, Spatial SwiGLU hidden 3072, 1024x2048 images
+    (64x128 = 8192 tokens), batch 32 in total sharded across the ranks (strong scaling), random-init
+    weights, pixels ~ U(0,1).  One CUDA graph per rank; no collective on the data path."""
+    from gtr_b200.backbone import GTRBackbone, GraphedBackbone
+    dev = torch.device("cuda", local_rank)
+    total_batch = 32
+    if total_batch % world:
+        return {"unavailable": f"batch {total_batch} does not divide over {world} ranks"}
+    b = total_batch // world
+    torch.manual_seed(0)
+    model = GTRBackbone().half().to(dev).eval()
+    runner = GraphedBackbone(model)
+    img = torch.rand(b, 3, 1024, 2048, generator=torch.Generator().manual_seed(rank)).half().to(dev)
+    steps = args.backbone_steps
+    for _ in range(3):
+        out = runner(img)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = runner(img)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    finite = bool(torch.isfinite(out[-1]).all())
+    sec = ms.item() * 1e-3
+    img_s = total_batch * steps / sec
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak_tf, kind = float(json.load(f)["bf16_tflops_sustained"]), "of measured"
+    except Exception:
+        peak_tf, kind = 1400.0, "of fallback"
+    tf_per_gpu = backbone_flops_per_image() * img_s / world / 1e12
+    return {"metric": "backbone_img_per_s", "value": img_s, "unit": "img/s", "n_gpus": world, "scaling": "strong",
+            "batch_total": total_batch, "batch_per_gpu": b, "steps": steps, "ms_per_step": ms.item() / steps,
+            "image": [1024, 2048], "tokens": 8192, "finite": finite, "gla_launches_per_step": 12,
+            "roofline": {"bound": "tensor", "achieved": tf_per_gpu, "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": tf_per_gpu / peak_tf, "peak_kind": kind}}
+
+
 def run_ours(args, rank, local_rank, world):
     import torch.distributed as dist
     if not torch.cuda.is_available():
@@ -261,6 +314,12 @@ def run_ours(args, rank, local_rank, world):
     total_ms, e2e_ms, kern_ms = times.tolist()
 
     # ---- sanity: the timed output equals the oracle on a slice (cheap, outside the timed region)
+    backbone = None
+    if args.backbone_steps > 0:
+        try:
+            backbone = run_backbone(args, rank, local_rank, world, dist)
+        except Exception as e:   # reported, never hidden: the operator line below stays valid
+            backbone = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
     if rank == 0:
         from oracle import c_oracle
         i = args.steps - 1
@@ -289,7 +348,7 @@ def run_ours(args, rank, local_rank, world):
                                        f"recurrence, median of {cpu_runs} runs ({cpu_med:.2f} s each)"},
             "e2e": {"value": world * tokens_per_step * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes, "steps": e2e_steps},
-            "gpu_launches": args.steps, "clocks": clocks, "parity_check": parity,
+            "gpu_launches": args.steps, "clocks": clocks, "parity_check": parity, "backbone": backbone,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -302,6 +361,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--backbone-steps", type=int, default=5,
+                    help="timed steps of the full synthetic backbone (reported under 'backbone'); 0 skips it")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     args = ap.parse_args()

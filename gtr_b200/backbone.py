@@ -1,0 +1,218 @@
+"""The GTR backbone pieces that sit either side of the GLA operator, in deploy form.
+
+Mirrors, for inference only, the reference's
+
+* ``GatedLinearAttention`` after ``convert_to_deploy`` (engine/gtr/backbone/vit_adapter.py:338-418
+  fused q/k/v/g/gk_low projection, :435-605 forward): one fused GEMM, the low-rank gate head,
+  the GLA operator with the RMSNorm * w * silu(g) epilogue, ``o_proj``;
+* ``SpatialSwiGLU`` in its split-GEMM deploy form (engine/gtr/backbone/vit_adapter_spatial_swiglu.py:21-70);
+* ``Block`` (vit_adapter.py:608-642) and the CLS-free ``VisionTransformerSpatialSwiGLU`` forward
+  (vit_adapter_spatial_swiglu.py:96-127) on top of the conv-pyramid patch-16 stem
+  (vit_adapter.py:188-204).
+
+What is different by design: the reference physically permutes the token sequence after every
+block (flip, and a grid transpose after odd blocks, vit_adapter_spatial_swiglu.py:88-94) so that
+block i scans the grid in order ``DIRECTIONS[i % 4]``.  Here tokens never move: block i passes
+``direction = i % 4`` to the operator, which folds the order into its tile coordinates, and the
+3x3 depthwise convolution of the MLP uses the kernel the reference's permuted grid implies
+(``oriented_dwconv_weight``).  q, k, v and the output gate are strided views of the fused GEMM
+output -- no contiguous copies -- and the gate logits go to the kernel raw (gk_normalizer).
+
+There is no fallback path: fp16 CUDA tensors and head dims K = V = 64 only.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+
+HEAD_DIM = 64
+
+
+def oriented_dwconv_weight(w: torch.Tensor, direction: int) -> torch.Tensor:
+    """Depthwise 3x3 kernel to apply on the canonical grid so that the result equals the
+    reference's convolution on the grid as block ``direction`` sees it: reversed scans view the
+    grid rotated by 180 degrees, column scans view it transposed."""
+    d = ops._direction_id(direction)
+    if d >= 2:
+        w = w.transpose(-1, -2)
+    if d & 1:
+        w = w.flip(-1, -2)
+    return w.contiguous()
+
+
+class GatedLinearAttention(nn.Module):
+    def __init__(self, hidden_size: int, num_heads: int, expand_k: float = 1.0, expand_v: float = 1.0,
+                 gate_low_rank_dim: int = 16, gate_logit_normalizer: float = 16.0, norm_eps: float = 1e-5):
+        super().__init__()
+        self.hidden_size, self.num_heads = hidden_size, num_heads
+        self.key_dim, self.value_dim = int(hidden_size * expand_k), int(hidden_size * expand_v)
+        if self.key_dim != num_heads * HEAD_DIM or self.value_dim != num_heads * HEAD_DIM:
+            raise ValueError("gtr_b200 serves head dims K = V = 64 only "
+                             f"(got K = {self.key_dim / num_heads:g}, V = {self.value_dim / num_heads:g})")
+        self.split = (self.key_dim, self.key_dim, self.value_dim, self.value_dim, gate_low_rank_dim)
+        self.qkv_g_gkl_proj = nn.Linear(hidden_size, sum(self.split), bias=False)
+        self.gk_high_proj = nn.Linear(gate_low_rank_dim, self.key_dim, bias=True)
+        self.g_norm_weight = nn.Parameter(torch.ones(HEAD_DIM))
+        self.o_proj = nn.Linear(self.value_dim, hidden_size, bias=False)
+        self.gate_logit_normalizer = float(gate_logit_normalizer)
+        self.norm_eps = float(norm_eps)
+        self.scale = HEAD_DIM ** -0.5
+        self._ws_key = None
+        self._ws = self._out = None
+
+    def _gla_buffers(self, B: int, T: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Workspace and output are kept per shape so that captured graphs see stable pointers
+        (reference: _get_or_make_gla_ws, vit_adapter.py:420-433)."""
+        key = (B, T, device)
+        if self._ws_key != key:
+            self._ws = ops.make_workspace(B, T, self.num_heads, device)
+            self._out = torch.empty(B, T, self.num_heads, HEAD_DIM, dtype=torch.float16, device=device)
+            self._ws_key = key
+        return self._ws, self._out
+
+    def forward(self, x: torch.Tensor, direction: int = 0, grid_hw: Optional[Tuple[int, int]] = None):
+        if not x.is_cuda or x.dtype != torch.float16:
+            raise RuntimeError("gtr_b200.GatedLinearAttention runs fp16 on CUDA only (no fallback path)")
+        B, T, _ = x.shape
+        H = self.num_heads
+        fused = self.qkv_g_gkl_proj(x)
+        q, k, v, g, gkl = fused.split(self.split, dim=-1)
+        gk = self.gk_high_proj(gkl)                               # raw gate logits [B, T, key_dim]
+        view = lambda t: t.unflatten(-1, (H, HEAD_DIM))           # strided views, no copies
+        ws, out = self._gla_buffers(B, T, x.device)
+        ops.chunk_gla_run_gated(view(q), view(k), view(v), view(gk), view(g), self.g_norm_weight, self.scale,
+                                self.norm_eps, ws, out, self.gate_logit_normalizer, direction=direction,
+                                grid_hw=grid_hw)
+        return self.o_proj(out.flatten(-2))
+
+
+class SpatialSwiGLU(nn.Module):
+    """SwiGLU whose value branch passes a 3x3 depthwise convolution on the patch grid."""
+
+    def __init__(self, hidden_size: int, hidden_ratio: int = 4, direction: int = 0):
+        super().__init__()
+        inter = int(hidden_size * hidden_ratio * 2 / 3)
+        inter = 256 * ((inter + 255) // 256)                      # vit_adapter_spatial_swiglu.py:28-30
+        self.intermediate_size = inter
+        self.direction = ops._direction_id(direction)
+        self.gate_w = nn.Parameter(torch.empty(inter, hidden_size))
+        self.value_w = nn.Parameter(torch.empty(inter, hidden_size))
+        self.dwconv = nn.Conv2d(inter, inter, 3, padding=1, groups=inter)
+        self.down_proj = nn.Linear(inter, hidden_size, bias=False)
+        nn.init.normal_(self.gate_w, std=0.02)
+        nn.init.normal_(self.value_w, std=0.02)
+
+    def load_reference_dwconv(self, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> None:
+        """Take the reference's depthwise weight (applied there on the permuted grid)."""
+        with torch.no_grad():
+            self.dwconv.weight.copy_(oriented_dwconv_weight(weight, self.direction))
+            if bias is not None:
+                self.dwconv.bias.copy_(bias)
+
+    def forward(self, x: torch.Tensor, grid_hw: Tuple[int, int]) -> torch.Tensor:
+        B, L, _ = x.shape
+        hg, wg = grid_hw
+        gate = F.linear(x, self.gate_w)
+        y = F.linear(x, self.value_w)                              # [B, L, C]
+        y = y.view(B, hg, wg, -1).permute(0, 3, 1, 2)              # channels-last view of [B, C, hg, wg]
+        y = self.dwconv(y)
+        y = y.permute(0, 2, 3, 1).reshape(B, L, -1)
+        return self.down_proj(F.silu(gate) * y)
+
+
+class Block(nn.Module):
+    def __init__(self, dim: int, num_heads: int, mlp_ratio: int, direction: int, expand_k: float = 1.0):
+        super().__init__()
+        self.direction = ops._direction_id(direction)
+        self.norm1 = nn.LayerNorm(dim, eps=1e-6)
+        self.attn = GatedLinearAttention(dim, num_heads, expand_k=expand_k)
+        self.norm2 = nn.LayerNorm(dim, eps=1e-6)
+        self.mlp = SpatialSwiGLU(dim, hidden_ratio=mlp_ratio, direction=direction)
+
+    def forward(self, x: torch.Tensor, grid_hw: Tuple[int, int]) -> torch.Tensor:
+        x = x + self.attn(self.norm1(x), self.direction, grid_hw)
+        return x + self.mlp(self.norm2(x), grid_hw)
+
+
+class ConvPyramidPatchEmbed(nn.Module):
+    """Patch-16 stem: three stride-2 3x3 conv + ReLU stages (BatchNorm folded, as after the
+    reference's convert_to_deploy) and a stride-2 projection."""
+
+    def __init__(self, embed_dim: int):
+        super().__init__()
+        chans = [embed_dim // 8, embed_dim // 4, embed_dim // 2]
+        self.convs = nn.ModuleList(nn.Conv2d(i, o, 3, 2, padding=1, bias=True) for i, o in zip([3] + chans[:-1], chans))
+        self.proj = nn.Conv2d(chans[-1], embed_dim, 3, 2, padding=1)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        for conv in self.convs:
+            x = F.relu(conv(x))
+        return self.proj(x).flatten(2).transpose(1, 2)
+
+
+class GTRBackbone(nn.Module):
+    """Stem + `depth` blocks; block i scans in order DIRECTIONS[i % 4] (vit_adapter.py:896-898)."""
+
+    def __init__(self, embed_dim: int = 768, depth: int = 12, num_heads: int = 12, mlp_ratio: int = 6,
+                 return_layers: Sequence[int] = (3, 7, 11), patch_size: int = 16, expand_k: float = 1.0):
+        super().__init__()
+        if patch_size != 16:
+            raise ValueError("the conv-pyramid stem is patch-16")
+        self.embed_dim, self.depth, self.patch_size = embed_dim, depth, patch_size
+        self.return_layers = tuple(return_layers)
+        self.patch_embed = ConvPyramidPatchEmbed(embed_dim)
+        self.blocks = nn.ModuleList(Block(embed_dim, num_heads, mlp_ratio, i % 4, expand_k) for i in range(depth))
+        self.apply(self._init)
+
+    @staticmethod
+    def _init(m):
+        if isinstance(m, nn.Linear):                               # vit_adapter.py:745-751
+            nn.init.normal_(m.weight, std=0.02)
+            if m.bias is not None:
+                nn.init.zeros_(m.bias)
+
+    def forward(self, img: torch.Tensor) -> List[torch.Tensor]:
+        hg, wg = img.shape[-2] // self.patch_size, img.shape[-1] // self.patch_size
+        x = self.patch_embed(img)
+        outs = []
+        for i, blk in enumerate(self.blocks):
+            x = blk(x, (hg, wg))
+            if i in self.return_layers:
+                outs.append(x)                                     # canonical token order at every layer
+        return outs
+
+
+class GraphedBackbone:
+    """Replays one captured CUDA graph per input shape (the reference benchmarks its model the same
+    way, tools/benchmark/torch_speed_fullgraph.py:134-158).  The operator's launches (a memset and one
+    kernel per block) are captured like any other stream work."""
+
+    def __init__(self, model: GTRBackbone):
+        self.model = model.eval()
+        self._graphs = {}
+
+    @torch.no_grad()
+    def __call__(self, img: torch.Tensor) -> List[torch.Tensor]:
+        key = (tuple(img.shape), img.device)
+        if key not in self._graphs:
+            static_in = img.clone()
+            side = torch.cuda.Stream(device=img.device)
+            side.wait_stream(torch.cuda.current_stream(img.device))
+            with torch.cuda.stream(side):
+                for _ in range(2):                                  # warm-up: allocations, tensor-map cache
+                    self.model(static_in)
+            torch.cuda.current_stream(img.device).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_out = self.model(static_in)
+            self._graphs[key] = (graph, static_in, static_out)
+        graph, static_in, static_out = self._graphs[key]
+        static_in.copy_(img, non_blocking=True)
+        graph.replay()
+        return static_out

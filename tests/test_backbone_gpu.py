@@ -1,0 +1,72 @@
+"""The backbone that keeps tokens in place and passes scan directions to the operator, against a
+CPU restatement of the reference's forward that physically permutes tokens between blocks."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def small_model():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from gtr_b200.backbone import GTRBackbone
+    torch.manual_seed(0)
+    m = GTRBackbone(embed_dim=128, depth=4, num_heads=2, mlp_ratio=6, return_layers=(1, 2, 3)).eval()
+    with torch.no_grad():                        # keep gates and norm weights away from trivial values
+        for blk in m.blocks:
+            blk.attn.g_norm_weight.uniform_(0.5, 1.5)
+            blk.attn.gk_high_proj.bias.normal_(0, 1.0)
+    return m
+
+
+def test_backbone_matches_reference_style_forward(small_model):
+    from oracle import backbone_ref, gla_ref
+    img = torch.rand(2, 3, 192, 192, generator=torch.Generator().manual_seed(1))      # 12 x 12 patch grid
+    want = backbone_ref.forward(copy.deepcopy(small_model).float(), img)
+    dev = copy.deepcopy(small_model).half().cuda()
+    with torch.no_grad():
+        got = dev(img.half().cuda())
+    assert len(got) == len(want) == 3
+    for w, g in zip(want, got):
+        m = gla_ref.error_metrics(w, g.float().cpu())
+        # an fp16 model (weights, GEMMs, LayerNorm, conv) against an fp32 one: a few 1e-3; a wrong scan
+        # order or a wrongly oriented depthwise kernel shows up as an error of order one
+        assert m["finite"] and m["rel_l2"] < 1.5e-2, m
+
+
+def test_wrong_scan_order_is_detected(small_model):
+    """Negative control for the tolerance above."""
+    from oracle import backbone_ref, gla_ref
+    img = torch.rand(1, 3, 192, 192, generator=torch.Generator().manual_seed(2))
+    want = backbone_ref.forward(copy.deepcopy(small_model).float(), img)
+    dev = copy.deepcopy(small_model).half().cuda()
+    dev.blocks[1].direction = 0                               # should be 1 (row reversed)
+    with torch.no_grad():
+        got = dev(img.half().cuda())
+    assert gla_ref.error_metrics(want[-1], got[-1].float().cpu())["rel_l2"] > 0.1
+
+
+def test_graph_replay_equals_eager(small_model):
+    from gtr_b200.backbone import GraphedBackbone
+    dev = copy.deepcopy(small_model).half().cuda()
+    img = torch.rand(1, 3, 256, 320, device="cuda").half()      # 16 x 20 grid: non-square
+    with torch.no_grad():
+        eager = [t.clone() for t in dev(img)]
+    graphed = GraphedBackbone(dev)
+    for _ in range(2):
+        out = graphed(img)
+    torch.cuda.synchronize()
+    for a, b in zip(eager, out):
+        assert torch.equal(a, b)
+
+
+def test_rejects_cpu_and_other_head_dims():
+    from gtr_b200.backbone import GatedLinearAttention
+    with pytest.raises(ValueError):
+        GatedLinearAttention(192, 6, expand_k=0.5)              # K = 16 per head
+    att = GatedLinearAttention(128, 2)
+    with pytest.raises(RuntimeError):
+        att(torch.zeros(1, 64, 128))
