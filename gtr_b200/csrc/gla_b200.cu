@@ -228,6 +228,9 @@ const char* gla_b200_strerror(int code) {
         case GLA_B200_ERR_CUDA: return "a CUDA call failed (see gla_b200_last_cuda_error)";
         case GLA_B200_ERR_TIMEOUT: return "a bounded wait inside the kernel expired; outputs are undefined";
         case GLA_B200_ERR_ARG: return "invalid argument";
+        case GLA_B200_ERR_STATIC_SCRATCH:
+            return "the problem needs more scratch than the library's built-in array (GLA_B200_STATIC_SCRATCH_BYTES); "
+                   "use gla_b200_forward with a caller-owned workspace";
         default: return "unknown gla_b200 error code";
     }
 }
@@ -413,3 +416,51 @@ int32_t gla_b200_trt_enqueue(const void* const* inputs, int32_t n_inputs, void* 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Forward without any caller-provided or allocated scratch.
+//
+// For hosts that must not touch the device allocator when they call the operator: an inference
+// server that handed all device memory to its own pool at start-up (a cudaMalloc there fails or
+// stalls every stream of the process), a plugin whose framework gives it no workspace, or a
+// real-time loop whose memory budget was fixed before it started.  The kernel's scratch (ticket,
+// status word, per-segment flags, segment aggregates and inclusive states) then lives in the array
+// below, which every GPU that loads this library holds until the process exits.
+//
+// In host code the array's name is only a handle, not a device address, so the address is looked
+// up with cudaGetSymbolAddress, once per device and with that device current.  That happens in the
+// first call on a device: make that call before any stream capture.
+// All calls share the one array per device; it keeps the previous call's contents.  The words that
+// must start at zero (ticket, status, flags) are cleared on the stream at the start of every call;
+// everything else is written before it is read.  Two calls that overlap on the same GPU (different
+// streams, or graph branches) would race on the array: serialise them.
+static __device__ __align__(256) unsigned char g_static_scratch[GLA_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+void* g_static_ptr[64] = {nullptr};
+}  // namespace
+
+extern "C" int gla_b200_forward_static(const gla_b200_args* a, void* stream) {
+    if (!a) return GLA_B200_ERR_NULL;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { note_cuda("cudaGetDevice", e); return GLA_B200_ERR_CUDA; }
+    if (dev < 0 || dev >= 64) return GLA_B200_ERR_DEVICE;
+    void* ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mu);
+        if (g_static_ptr[dev] == nullptr) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_static_scratch);      // address on the current device
+            if (e != cudaSuccess || p == nullptr) { note_cuda("cudaGetSymbolAddress", e); return GLA_B200_ERR_CUDA; }
+            g_static_ptr[dev] = p;
+        }
+        ptr = g_static_ptr[dev];
+    }
+    gla_b200_args b = *a;
+    b.workspace = ptr;
+    b.workspace_bytes = GLA_B200_STATIC_SCRATCH_BYTES;
+    const int rc = gla_b200_forward(&b, stream);
+    return rc == GLA_B200_ERR_WORKSPACE ? GLA_B200_ERR_STATIC_SCRATCH : rc;
+}

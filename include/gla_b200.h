@@ -51,7 +51,8 @@ enum gla_b200_error {
     GLA_B200_ERR_DEVICE = -6,        /* not an sm_100 device, or driver entry point unavailable */
     GLA_B200_ERR_CUDA = -7,          /* a CUDA runtime/driver call failed (see gla_b200_last_cuda_error) */
     GLA_B200_ERR_TIMEOUT = -8,       /* device status word: a bounded wait inside the kernel expired */
-    GLA_B200_ERR_ARG = -9            /* any other invalid argument */
+    GLA_B200_ERR_ARG = -9,           /* any other invalid argument */
+    GLA_B200_ERR_STATIC_SCRATCH = -10 /* gla_b200_forward_static: problem exceeds the built-in scratch array */
 };
 
 typedef struct gla_b200_args {
@@ -78,7 +79,7 @@ typedef struct gla_b200_args {
     float scale;                     /* applied to the output, reference default K^-0.5 */
     float gk_normalizer;             /* 0: g is a log gate; >0: g holds logits */
     float rms_eps;
-    uint32_t wait_limit;             /* polls before a device-side wait gives up; 0 = default */
+    uint32_t wait_limit;             /* microseconds before a device-side wait gives up; 0 = 2 s */
 } gla_b200_args;
 
 /* Replaces chunk_gla_run / chunk_gla_run_gated (gla_torch_ext.cu:40-154) and
@@ -86,6 +87,20 @@ typedef struct gla_b200_args {
  * (a cudaStream_t), never synchronises, never allocates; capturable in a CUDA graph once
  * the calling thread has run the same shape once.  Returns 0 or a gla_b200_error. */
 int gla_b200_forward(const gla_b200_args* args, void* stream);
+
+/* Same operator, but with nothing allocated and no workspace from the caller (`workspace` and
+ * `workspace_bytes` of `args` are ignored): the scratch is a fixed array of
+ * GLA_B200_STATIC_SCRATCH_BYTES inside the library, one per GPU, held until the process exits.
+ * It is meant for callers that cannot reach the device allocator at call time -- a server whose
+ * memory pool owns the whole GPU, a plugin that is handed no workspace, a loop with a frozen memory
+ * budget.  No counterpart in the reference (its callers always bring a workspace tensor).
+ * The first call on a device looks up the array's device address; issue it before any stream
+ * capture.  The array is shared by all calls on that GPU and keeps the last call's contents (the
+ * words that must be zero are cleared at the start of each call), so calls that overlap on one GPU
+ * race: run them one after another.  Problems whose segmentation needs more than the array return
+ * GLA_B200_ERR_STATIC_SCRATCH; every automatic segmentation on a 148-SM GPU fits. */
+#define GLA_B200_STATIC_SCRATCH_BYTES (24u << 20)
+int gla_b200_forward_static(const gla_b200_args* args, void* stream);
 
 /* Replaces workspace_floats (gla_torch_ext.cu:24-33); bytes, not floats.  0 on bad shape. */
 size_t gla_b200_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_t K, int32_t V);
