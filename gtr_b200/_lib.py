@@ -37,7 +37,7 @@ class Args(ctypes.Structure):
 EXPORTS = (
     "gla_b200_forward", "gla_b200_workspace_bytes", "gla_b200_check_status", "gla_b200_rmsnorm_gated",
     "gla_b200_trt_enqueue", "gla_b200_strerror", "gla_b200_last_cuda_error", "gla_b200_version",
-    "gla_b200_forward_static",
+    "gla_b200_forward_static", "gla_b200_selftest_wait_timeout",
 )
 
 _lib = None
@@ -62,6 +62,8 @@ def lib() -> ctypes.CDLL:
     L.gla_b200_forward.restype = ctypes.c_int
     L.gla_b200_forward_static.argtypes = [ctypes.POINTER(Args), ctypes.c_void_p]
     L.gla_b200_forward_static.restype = ctypes.c_int
+    L.gla_b200_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint32, ctypes.c_void_p]
+    L.gla_b200_selftest_wait_timeout.restype = ctypes.c_int
     L.gla_b200_workspace_bytes.argtypes = [ctypes.c_int32] * 5
     L.gla_b200_workspace_bytes.restype = ctypes.c_size_t
     L.gla_b200_check_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]

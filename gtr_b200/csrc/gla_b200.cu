@@ -365,6 +365,24 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     return GLA_B200_OK;
 }
 
+int gla_b200_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint32_t limit_us, void* stream_v) {
+    if (!workspace) return GLA_B200_ERR_NULL;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < 512) return GLA_B200_ERR_WORKSPACE;
+    if (limit_us == 0 || limit_us > 1000000u) return GLA_B200_ERR_ARG;      // a self-test never waits longer than 1 s
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    cudaError_t e = cudaMemsetAsync(workspace, 0, 512, stream);
+    if (e != cudaSuccess) { note_cuda("cudaMemsetAsync", e); return GLA_B200_ERR_CUDA; }
+    gla::Params P;
+    memset(&P, 0, sizeof(P));
+    P.ctrl = static_cast<uint32_t*>(workspace);
+    P.flags = P.ctrl + 64;
+    P.wait_limit_us = limit_us;
+    gla::wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(P);
+    e = cudaPeekAtLastError();
+    if (e != cudaSuccess) { note_cuda("self-test launch", e); return GLA_B200_ERR_CUDA; }
+    return GLA_B200_OK;
+}
+
 int gla_b200_check_status(const void* workspace, void* stream) {
     if (!workspace) return GLA_B200_ERR_NULL;
     uint32_t ctrl[2] = {0, 0};

@@ -377,6 +377,39 @@ __device__ __forceinline__ void store_row_f16(uint32_t tile, uint32_t row, uint3
     }
 }
 
+// Self-test of the bounded waits: one warp waits on an mbarrier nobody arrives at and on a global
+// flag nobody sets.  Both waits must give up after the limit, set the status word and return.
+__global__ void wait_timeout_selftest_kernel(Params P) {
+    __shared__ Misc M;
+    Ctx ctx;
+    ctx.p = &P;
+    ctx.misc = &M;
+    ctx.base = nullptr;
+    ctx.smem = 0;
+    ctx.deadline_span_ns = static_cast<uint64_t>(P.wait_limit_us) * 1000ull;
+#ifdef GLA_TRACE
+    uint32_t trace_n = 0;
+    ctx.trace_n = &trace_n;
+#endif
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&M.full[0]), 1);
+        M.abort = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    mbar_wait(ctx, &M.full[0], 0);                 // never completes: returns after the limit
+    const uint64_t t0 = globaltimer_ns();
+    while (ld_acquire_gpu(P.flags) == 0u) {        // never set: same exit rule as the look-back
+        if (globaltimer_ns() - t0 > ctx.deadline_span_ns) {
+            raise_timeout(ctx, WHERE_LOOKBACK);
+            break;
+        }
+        __nanosleep(64);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) P.ctrl[2] = M.abort;     // 1: the CTA noticed the time-out
+}
+
 struct ItemInfo {
     int seq, seg, b, h, first_chunk, nchunks, state_pass;
 };

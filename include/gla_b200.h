@@ -110,6 +110,12 @@ size_t gla_b200_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_t K, int3
  * The reference has no counterpart (its waits are unbounded, gla_chunk.cuh:1229-1233). */
 int gla_b200_check_status(const void* workspace, void* stream);
 
+/* Exercises the kernel's bounded waits without any real work: one warp waits on a barrier and on a
+ * flag that nothing ever completes, with a limit of `limit_us` microseconds (<= 1 s).  Afterwards
+ * gla_b200_check_status(workspace) must report GLA_B200_ERR_TIMEOUT and the context stays usable.
+ * No counterpart in the reference, whose device-side waits are unbounded. */
+int gla_b200_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint32_t limit_us, void* stream);
+
 /* Replaces rmsnorm_gated (gla_torch_ext.cu:156-196, kernel gla_norm_gate.cuh:13-75):
  * y = x * rsqrt(mean(x^2) + eps) * w * silu(g) over rows of D = 64 fp16 values; y may alias x. */
 int gla_b200_rmsnorm_gated(const void* x, const void* g, const void* w, void* y,

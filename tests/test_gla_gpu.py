@@ -305,3 +305,25 @@ def test_fused_rmsnorm_swish_gate_epilogue(G, direction, grid, T):
     G.rmsnorm_gated(o, gate.cuda(), w.cuda(), o, 1e-5)
     m2 = gla_ref.error_metrics(y_ref, o.float().cpu())
     assert m2["finite"] and m2["rel_l2"] <= 2 * REL_L2, m2
+
+
+def test_bounded_waits_time_out_cleanly(G):
+    """A wait that nothing satisfies gives up after its limit, sets the status word, and the context
+    stays usable (no trap, no hang): the operator runs correctly right afterwards."""
+    import ctypes
+    from gtr_b200 import _lib
+    from oracle import c_oracle, gla_ref
+    ws = G.make_workspace(1, 256, 2, "cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = _lib.lib().gla_b200_selftest_wait_timeout(ws.data_ptr(), ws.numel() * 4, 20000, stream)   # 20 ms
+    assert rc == 0
+    with pytest.raises(_lib.GlaError) as err:
+        G.check_status(ws)
+    assert err.value.code == _lib.ERR_TIMEOUT
+    assert int(ws.view(torch.int32)[2].item()) == 1
+    q, k, v, g = gla_ref.make_inputs(1, 256, 2, seed=1)
+    o = torch.empty(1, 256, 2, 64, dtype=torch.float16, device="cuda")
+    G.chunk_gla_run(q.cuda(), k.cuda(), v.cuda(), g.cuda(), 0.125, ws, o)
+    G.check_status(ws)                                     # cleared by the new launch
+    ref, _ = c_oracle.forward(q, k, v, g)
+    _check(ref, o.float().cpu())
