@@ -145,11 +145,15 @@ __device__ __forceinline__ void raise_timeout(const Ctx& c, uint32_t where) {
 // Bounded wait.  After a time-out in this CTA every later wait returns at once, so all warps
 // keep following the protocol (arrivals, named barriers) and the CTA drains and exits; the
 // result is then undefined and the status word says so.
+#ifndef GLA_SPIN_SLEEP_NS
+#define GLA_SPIN_SLEEP_NS 100
+#endif
 __device__ __noinline__ void mbar_wait_slow(const Ctx& c, uint32_t b, uint32_t parity) {
     const uint64_t t0 = globaltimer_ns();
     uint32_t n = 0;
     while (true) {
         if (mbar_try_wait(b, parity)) return;
+        __nanosleep(GLA_SPIN_SLEEP_NS);   // a sleeping warp issues nothing; a polling one competes with working warps
         if ((++n & 63u) == 0u) {
             if (c.misc->abort) return;
             if (globaltimer_ns() - t0 > c.deadline_span_ns) {
@@ -216,28 +220,89 @@ __device__ __noinline__ void logits_to_log_gates(uint8_t* tg, float inv_norm, in
 // the physical (shared-memory / TMEM) row is mirrored for reversed scans.  Tiles are rows of
 // 128 bytes whose 16-byte units are XOR-swizzled with (row & 7); since 8w is a multiple of 8
 // the swizzle of logical row i depends on i only, which is a compile-time constant here.
-__device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, int n, int valid, int w, int l,
-                                          bool state_only) {
-    constexpr int R = kRowsPerThread;
-    static_assert(R == 8, "the swizzle shortcut below needs 8 rows per thread");
-    const Params& P = *c.p;
-    Misc& M = *c.misc;
-    const int par = n & 1;
-    const bool rev = P.rev != 0;
-    // byte offset of (logical row 8w+i, channel 2l) in an fp16 tile = row0 + i*step + ((lx ^ i) << 4) + lb
-    const int row0 = rev ? (63 - R * w) * 128 : (R * w) * 128;
-    const int step = rev ? -128 : 128;
-    const uint32_t lx = rev ? ((l >> 2) ^ 7u) : (l >> 2);
-    const uint32_t lb = (l & 3u) << 2;
-    // tf32 tiles: channel 2l lives in half (l >> 4), 16-byte unit (l & 15) >> 1, byte (l & 1) * 8
-    const uint32_t ly = rev ? (((l & 15u) >> 1) ^ 7u) : ((l & 15u) >> 1);
-    const uint32_t lb32 = (l >> 4) * kTileBytes + ((l & 1u) << 3);
+//
+// The hot variants (full chunk, tf32 path) are straight-line code without branches between rows, so
+// that the eight independent rows can be interleaved by the instruction scheduler; ragged chunks
+// and chunks on the exact path take out-of-line rolled versions.
+struct GateLane {
+    uint32_t a16;    // byte offset of (logical row 8w, channel 2l) in an fp16 tile, without the swizzle term
+    uint32_t a32;    // same for the two-half tf32 tiles
+    uint32_t x16;    // swizzle term (16-byte unit index << 4) of logical row 8w, fp16 tiles
+    uint32_t x32;    // same, tf32 tiles
+};
+template <bool kRev>
+__device__ __forceinline__ GateLane gate_lane(int w, int l) {
+    GateLane g;
+    const uint32_t row0 = kRev ? (63u - 8u * w) : 8u * w;
+    g.a16 = row0 * 128u + ((l & 3u) << 2);
+    g.a32 = row0 * 128u + (l >> 4) * kTileBytes + ((l & 1u) << 3);
+    g.x16 = (kRev ? ((l >> 2) ^ 7u) : (l >> 2)) << 4;
+    g.x32 = (kRev ? (((l & 15u) >> 1) ^ 7u) : ((l & 15u) >> 1)) << 4;
+    return g;
+}
+// offsets of logical row 8w + i (i is a compile-time constant at every use)
+template <bool kRev> __device__ __forceinline__ uint32_t off16(const GateLane& g, int i) {
+    return (kRev ? g.a16 - 128u * i : g.a16 + 128u * i) + (g.x16 ^ (static_cast<uint32_t>(i) << 4));
+}
+template <bool kRev> __device__ __forceinline__ uint32_t off32(const GateLane& g, int i) {
+    return (kRev ? g.a32 - 128u * i : g.a32 + 128u * i) + (g.x32 ^ (static_cast<uint32_t>(i) << 4));
+}
+
+// Rolled, out-of-line row pass for the rare cases: a ragged last chunk (rows past `valid` are zeroed)
+// and chunks on the exact-score path (`wide`: G and raw q, k are stashed in plain layouts where the
+// tf32 operands would go).  Recomputes the running gate sum from the (still raw) gate tile.
+template <bool kRev>
+__device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, int valid, int w, int l, bool state_only,
+                                               bool wide, float off0, float off1, float b40, float b41, float e10,
+                                               float e11, float e20, float e21) {
+    const GateLane gl = gate_lane<kRev>(w, l);
     const uint32_t tq = stage, tk = stage + kTileBytes, tg = stage + 2 * kTileBytes, tv = stage + 3 * kTileBytes;
     const uint32_t qbar = c.smem + kOffQbar, kbar = c.smem + kOffKbar;
     const uint32_t c0 = 2u * l;
+    float a0 = off0, a1 = off1;
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t o16 = (kRev ? gl.a16 - 128u * i : gl.a16 + 128u * i) + (gl.x16 ^ (static_cast<uint32_t>(i) << 4));
+        const uint32_t o32 = (kRev ? gl.a32 - 128u * i : gl.a32 + 128u * i) + (gl.x32 ^ (static_cast<uint32_t>(i) << 4));
+        const bool live = 8 * w + i < valid;
+        const float2 gv = unpack_half2(lds32(tg + o16));
+        a0 += live ? gv.x * kLog2e : 0.f;
+        a1 += live ? gv.y * kLog2e : 0.f;
+        const uint32_t kr = live ? lds32(tk + o16) : 0u;
+        const uint32_t qr = (live && !state_only) ? lds32(tq + o16) : 0u;
+        const float2 kv = unpack_half2(kr), qv = unpack_half2(qr);
+        const float kh0 = kv.x * ex2(b40 - a0), kh1 = kv.y * ex2(b41 - a1);
+        sts32(tk + o16, pack_half2_sat(kh0, kh1));
+        if (!live) sts32(tv + o16, 0u);                // rows past the end must be finite for the MMAs
+        if (!state_only) {
+            const float qh0 = qv.x * ex2(a0), qh1 = qv.y * ex2(a1);
+            sts32(tq + o16, pack_half2_sat(qh0, qh1));
+            if (!wide) {
+                sts64(qbar + o32, round_tf32(qh0 * e10), round_tf32(qh1 * e11));
+                sts64(kbar + o32, round_tf32(kh0 * e20), round_tf32(kh1 * e21));
+            } else {   // plain layouts: G fp32 [64][64] at qbar; raw q, k fp16 [64][64] at kbar
+                const int rho = kRev ? 63 - (8 * w + i) : 8 * w + i;
+                sts64(qbar + rho * 256 + c0 * 4, a0, a1);
+                sts32(kbar + rho * 128 + c0 * 2, qr);
+                sts32(kbar + kTileBytes + rho * 128 + c0 * 2, kr);
+            }
+        }
+    }
+}
+
+template <bool kStateOnly, bool kRev>
+__device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, int n, int valid, int w, int l) {
+    constexpr int R = kRowsPerThread;
+    static_assert(R == 8, "the swizzle shortcut needs 8 rows per thread");
+    const Params& P = *c.p;
+    Misc& M = *c.misc;
+    const int par = n & 1;
+    const GateLane gl = gate_lane<kRev>(w, l);
+    const uint32_t tq = stage, tk = stage + kTileBytes, tg = stage + 2 * kTileBytes;
+    const uint32_t qbar = c.smem + kOffQbar, kbar = c.smem + kOffKbar;
+    const uint32_t c0 = 2u * l;
     const uint32_t tot_sa = smem_u32(&M.tot[par][0][c0]);   // + ww * kD * 4
-#define GLA_OFF16(i) (row0 + (i) * step + static_cast<int>(((lx ^ static_cast<uint32_t>(i)) << 4) + lb))
-#define GLA_OFF32(i) (row0 + (i) * step + static_cast<int>(((ly ^ static_cast<uint32_t>(i)) << 4) + lb32))
+    const bool ragged = valid < kChunk;
 
     GLA_EVC(c, 45);
     if (P.inv_norm > 0.f) {
@@ -246,21 +311,22 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, int n, i
     }
     uint32_t graw[R], kraw[R], qraw[R];
 #pragma unroll
-    for (int i = 0; i < R; ++i) graw[i] = lds32(tg + GLA_OFF16(i));
+    for (int i = 0; i < R; ++i) graw[i] = lds32(tg + off16<kRev>(gl, i));
+    if (!ragged) {
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-        kraw[i] = lds32(tk + GLA_OFF16(i));
-        qraw[i] = state_only ? 0u : lds32(tq + GLA_OFF16(i));
+        for (int i = 0; i < R; ++i) {
+            kraw[i] = lds32(tk + off16<kRev>(gl, i));
+            if (!kStateOnly) qraw[i] = lds32(tq + off16<kRev>(gl, i));
+        }
     }
     GLA_EVC(c, 44);
-    if (GLA_DBG(0)) { fence_proxy_async_smem(); return; }
     float cs0[R], cs1[R];
     {
         float a0 = 0.f, a1 = 0.f;
 #pragma unroll
         for (int i = 0; i < R; ++i) {
             const float2 gv = unpack_half2(graw[i]);
-            const bool live = R * w + i < valid;
+            const bool live = !ragged || R * w + i < valid;
             a0 += live ? gv.x * kLog2e : 0.f;
             a1 += live ? gv.y * kLog2e : 0.f;
             cs0[i] = a0;
@@ -283,7 +349,7 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, int n, i
     if (w == 0) sts64(smem_u32(&M.b4s[par][c0]), b40, b41);
     bool wide = false;
     float e10 = 0.f, e11 = 0.f, e20 = 0.f, e21 = 0.f;
-    if (!state_only) {
+    if (!kStateOnly) {
         wide = __any_sync(0xffffffffu, (-b40 > kWideLimit) || (-b41 > kWideLimit));
         if (w == 0 && l == 0) M.wide[par] = wide ? 1u : 0u;
         e10 = ex2(-gm0);
@@ -291,37 +357,51 @@ __device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, int n, i
         e20 = ex2(gm0 - b40);
         e21 = ex2(gm1 - b41);
     }
-    if (GLA_DBG(2)) { fence_proxy_async_smem(); return; }
+    if (ragged || wide) {
+        gate_rows_general<kRev>(c, stage, valid, w, l, kStateOnly, wide, off0, off1, b40, b41, e10, e11, e20, e21);
+    } else {
+        // straight-line: exponents first, then products, then stores
+        const float ck0 = b40 - off0, ck1 = b41 - off1;
+        float ek0[R], ek1[R], eq0[R], eq1[R];
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const bool live = R * w + i < valid;
-        const float G0 = off0 + cs0[i], G1 = off1 + cs1[i];
-        const uint32_t kr = live ? kraw[i] : 0u, qr = live ? qraw[i] : 0u;
-        const float2 kv = unpack_half2(kr);
-        const float kh0 = kv.x * ex2(b40 - G0), kh1 = kv.y * ex2(b41 - G1);
-        sts32(tk + GLA_OFF16(i), pack_half2_sat(kh0, kh1));
-        if (!live) sts32(tv + GLA_OFF16(i), 0u);   // rows past the end must be finite for the MMAs
-        if (!state_only) {
-            const float2 qv = unpack_half2(qr);
-            const float qh0 = qv.x * ex2(G0), qh1 = qv.y * ex2(G1);
-            sts32(tq + GLA_OFF16(i), pack_half2_sat(qh0, qh1));
-            if (GLA_DBG(1)) {
-            } else if (!wide) {
-                sts64(qbar + GLA_OFF32(i), round_tf32(qh0 * e10), round_tf32(qh1 * e11));
-                sts64(kbar + GLA_OFF32(i), round_tf32(kh0 * e20), round_tf32(kh1 * e21));
-            } else {  // exact path operands, plain layouts: G fp32 [64][64]; raw q, k fp16 [64][64]
-                const int rho = rev ? 63 - (R * w + i) : R * w + i;
-                sts64(qbar + rho * 256 + c0 * 4, G0, G1);
-                sts32(kbar + rho * 128 + c0 * 2, qr);
-                sts32(kbar + kTileBytes + rho * 128 + c0 * 2, kr);
+        for (int i = 0; i < R; ++i) {
+            ek0[i] = ex2(ck0 - cs0[i]);
+            ek1[i] = ex2(ck1 - cs1[i]);
+            if (!kStateOnly) {
+                eq0[i] = ex2(off0 + cs0[i]);
+                eq1[i] = ex2(off1 + cs1[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const float2 kv = unpack_half2(kraw[i]);
+            const float kh0 = kv.x * ek0[i], kh1 = kv.y * ek1[i];
+            sts32(tk + off16<kRev>(gl, i), pack_half2_sat(kh0, kh1));
+            if (!kStateOnly) {
+                const float2 qv = unpack_half2(qraw[i]);
+                const float qh0 = qv.x * eq0[i], qh1 = qv.y * eq1[i];
+                sts32(tq + off16<kRev>(gl, i), pack_half2_sat(qh0, qh1));
+                if (!GLA_DBG(1)) {
+                    sts64(qbar + off32<kRev>(gl, i), round_tf32(qh0 * e10), round_tf32(qh1 * e11));
+                    sts64(kbar + off32<kRev>(gl, i), round_tf32(kh0 * e20), round_tf32(kh1 * e21));
+                }
             }
         }
     }
-#undef GLA_OFF16
-#undef GLA_OFF32
     GLA_EVC(c, 42);
     fence_proxy_async_smem();
     GLA_EVC(c, 43);
+}
+
+__device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, int n, int valid, int w, int l,
+                                          bool state_only) {
+    if (c.p->rev) {
+        if (state_only) gate_math_t<true, true>(c, stage, n, valid, w, l);
+        else gate_math_t<false, true>(c, stage, n, valid, w, l);
+    } else {
+        if (state_only) gate_math_t<true, false>(c, stage, n, valid, w, l);
+        else gate_math_t<false, false>(c, stage, n, valid, w, l);
+    }
 }
 
 __device__ __forceinline__ uint32_t sw_f16(uint32_t row, uint32_t col) {     // col in fp16 elements
