@@ -9,7 +9,8 @@ import ctypes
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libgla_b200.so")
+# GTR_B200_LIB selects another build of the same library (e.g. one compiled with different tile parameters)
+LIB_PATH = os.environ.get("GTR_B200_LIB") or os.path.join(PKG, "libgla_b200.so")
 
 OK = 0
 ERR_TIMEOUT = -8

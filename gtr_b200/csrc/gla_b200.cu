@@ -298,7 +298,7 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     // segmentation
     const int NT = num_chunks(a->T);
     const int nseq = a->B * a->H;
-    int slots = 2 * di.sms;
+    int slots = gla::kCtasPerSm * di.sms;
     if (const char* e = getenv("GLA_B200_MAX_CTAS")) {   // tuning aid: cap the persistent grid
         const int cap = atoi(e);
         if (cap > 0 && cap < slots) slots = cap;

@@ -38,8 +38,18 @@ constexpr int kChunk = 64;
 constexpr int kD = 64;                    // K = V = 64
 constexpr int kTileBytes = kChunk * 128;  // one fp16 [64 x 64] tile
 constexpr int kStageBytes = 4 * kTileBytes;
-constexpr int kNumStages = 2;
-constexpr int kComputeWarps = 8;           // two warps per TMEM lane quadrant, each taking half the columns
+#ifndef GLA_MIN_CTAS
+#define GLA_MIN_CTAS 2
+#endif
+#ifndef GLA_STAGES
+#define GLA_STAGES 2
+#endif
+#ifndef GLA_COMPUTE_WARPS
+#define GLA_COMPUTE_WARPS 8
+#endif
+constexpr int kCtasPerSm = GLA_MIN_CTAS;    // resident CTAs per SM the launch bounds and the grid size assume
+constexpr int kNumStages = GLA_STAGES;
+constexpr int kComputeWarps = GLA_COMPUTE_WARPS;   // kComputeWarps/4 warps per TMEM lane quadrant, splitting its columns
 constexpr int kComputeThreads = 32 * kComputeWarps;
 constexpr int kThreads = kComputeThreads + 64;
 constexpr int kRowsPerThread = kChunk / kComputeWarps;   // gate math: logical rows per thread
@@ -101,7 +111,7 @@ constexpr int kOffQbar = kNumStages * kStageBytes;       // 16 KB tf32 (two 8 KB
 constexpr int kOffKbar = kOffQbar + 2 * kTileBytes;
 constexpr int kOffS16 = kOffKbar + 2 * kTileBytes;
 constexpr int kOffMisc = kOffS16 + kTileBytes;
-constexpr int kMiscBytes = 6144;
+constexpr int kMiscBytes = 4096 + 512 * kComputeWarps;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + alignment slack
 
 struct Misc {
@@ -233,11 +243,16 @@ struct GateLane {
 template <bool kRev>
 __device__ __forceinline__ GateLane gate_lane(int w, int l) {
     GateLane g;
-    const uint32_t row0 = kRev ? (63u - 8u * w) : 8u * w;
+    constexpr uint32_t R = kRowsPerThread;
+    const uint32_t first = R * w;                                   // first logical row of this thread
+    const uint32_t row0 = kRev ? (63u - first) : first;
+    // (physical row & 7) of logical row first + i is ((first & 7) + i) forward and 7 - that reversed; R
+    // divides 8, so (first & 7) and i < R occupy different bits and the sum is an XOR
+    const uint32_t rbits = (first & 7u) ^ (kRev ? 7u : 0u);
     g.a16 = row0 * 128u + ((l & 3u) << 2);
     g.a32 = row0 * 128u + (l >> 4) * kTileBytes + ((l & 1u) << 3);
-    g.x16 = (kRev ? ((l >> 2) ^ 7u) : (l >> 2)) << 4;
-    g.x32 = (kRev ? (((l & 15u) >> 1) ^ 7u) : ((l & 15u) >> 1)) << 4;
+    g.x16 = ((l >> 2) ^ rbits) << 4;
+    g.x32 = (((l & 15u) >> 1) ^ rbits) << 4;
     return g;
 }
 // offsets of logical row 8w + i (i is a compile-time constant at every use)
@@ -261,10 +276,10 @@ __device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, int
     const uint32_t c0 = 2u * l;
     float a0 = off0, a1 = off1;
 #pragma unroll 1
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < kRowsPerThread; ++i) {
         const uint32_t o16 = (kRev ? gl.a16 - 128u * i : gl.a16 + 128u * i) + (gl.x16 ^ (static_cast<uint32_t>(i) << 4));
         const uint32_t o32 = (kRev ? gl.a32 - 128u * i : gl.a32 + 128u * i) + (gl.x32 ^ (static_cast<uint32_t>(i) << 4));
-        const bool live = 8 * w + i < valid;
+        const bool live = kRowsPerThread * w + i < valid;
         const float2 gv = unpack_half2(lds32(tg + o16));
         a0 += live ? gv.x * kLog2e : 0.f;
         a1 += live ? gv.y * kLog2e : 0.f;
@@ -281,7 +296,7 @@ __device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, int
                 sts64(qbar + o32, round_tf32(qh0 * e10), round_tf32(qh1 * e11));
                 sts64(kbar + o32, round_tf32(kh0 * e20), round_tf32(kh1 * e21));
             } else {   // plain layouts: G fp32 [64][64] at qbar; raw q, k fp16 [64][64] at kbar
-                const int rho = kRev ? 63 - (8 * w + i) : 8 * w + i;
+                const int rho = kRev ? 63 - (kRowsPerThread * w + i) : kRowsPerThread * w + i;
                 sts64(qbar + rho * 256 + c0 * 4, a0, a1);
                 sts32(kbar + rho * 128 + c0 * 2, qr);
                 sts32(kbar + kTileBytes + rho * 128 + c0 * 2, kr);
@@ -293,7 +308,7 @@ __device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, int
 template <bool kStateOnly, bool kRev>
 __device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, int n, int valid, int w, int l) {
     constexpr int R = kRowsPerThread;
-    static_assert(R == 8, "the swizzle shortcut needs 8 rows per thread");
+    static_assert(R == 8 || R == 4, "the swizzle shortcut needs a row count that divides 8");
     const Params& P = *c.p;
     Misc& M = *c.misc;
     const int par = n & 1;
@@ -441,8 +456,12 @@ __device__ __forceinline__ void tmem_row(uint32_t tmem_base, int w, uint32_t col
     const uint32_t addr = tmem_base + (static_cast<uint32_t>(32 * w) << 16) + col;
     uint32_t* r = reinterpret_cast<uint32_t*>(x);
     __syncwarp();   // tcgen05.ld is warp-collective; lane 0 may come from a single-thread branch
+    if constexpr (N == 8) {
+        tmem_ld8(addr, r);
+    } else {
 #pragma unroll
-    for (int k = 0; k < N / 16; ++k) tmem_ld16(addr + 16 * k, r + 16 * k);
+        for (int k = 0; k < N / 16; ++k) tmem_ld16(addr + 16 * k, r + 16 * k);
+    }
     tmem_ld_wait();
 }
 
@@ -507,7 +526,7 @@ __device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
     return it;
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params P) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -560,7 +579,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     const uint32_t tmem = M.tmem_base;
 
     // use counters of every barrier, kept per role (all roles see the same sequence of uses)
-    uint32_t n_full[kNumStages] = {0, 0}, n_empty[kNumStages] = {0, 0};
+    uint32_t n_full[kNumStages] = {}, n_empty[kNumStages] = {};
     uint32_t n_ops = 0, n_adone = 0, n_a16 = 0, n_osdone = 0, n_accfree = 0, n_s16 = 0;
     uint32_t chunk_ctr = 0;   // chunks processed by this CTA so far: stage = ctr % 2, parity slot = ctr & 1
 
