@@ -26,8 +26,8 @@
 // therefore owns useful data: lanes 0-15 of warp w hold row 16w+l of O (and the left half of
 // A), lanes 16-31 hold state row 16w+l-16 (and the right half of A).
 //
-// Warp roles: warps 0-7 gate math, TMEM epilogues, state (warps w and w+4 share TMEM quadrant w
-// and split its columns); warp 8 TMA producer; warp 9 MMA issue.
+// Warp roles: warps 0-7 gate group (operand preparation), warps 8-15 epilogue group (TMEM read-out,
+// state; warps e and e+4 share TMEM quadrant e and split its columns), warp 16 TMA producer, warp 17 MMA issue.
 #pragma once
 
 #include "gla_device.cuh"
@@ -39,24 +39,28 @@ constexpr int kD = 64;                    // K = V = 64
 constexpr int kTileBytes = kChunk * 128;  // one fp16 [64 x 64] tile
 constexpr int kStageBytes = 4 * kTileBytes;
 #ifndef GLA_MIN_CTAS
-#define GLA_MIN_CTAS 2
+#define GLA_MIN_CTAS 1
 #endif
 #ifndef GLA_STAGES
-#define GLA_STAGES 2
+#define GLA_STAGES 4
 #endif
 #ifndef GLA_COMPUTE_WARPS
 #define GLA_COMPUTE_WARPS 8
 #endif
 constexpr int kCtasPerSm = GLA_MIN_CTAS;    // resident CTAs per SM the launch bounds and the grid size assume
 constexpr int kNumStages = GLA_STAGES;
-constexpr int kComputeWarps = GLA_COMPUTE_WARPS;   // kComputeWarps/4 warps per TMEM lane quadrant, splitting its columns
+// Two groups of kComputeWarps warps each: the gate group (operand preparation) and the epilogue group
+// (TMEM read-out, state).  In the epilogue group kComputeWarps/4 warps share a TMEM lane quadrant and
+// split its columns.
+constexpr int kComputeWarps = GLA_COMPUTE_WARPS;
 constexpr int kComputeThreads = 32 * kComputeWarps;
-constexpr int kThreads = kComputeThreads + 64;
+constexpr int kThreads = 2 * kComputeThreads + 64;
 constexpr int kRowsPerThread = kChunk / kComputeWarps;   // gate math: logical rows per thread
 constexpr int kColSplit = kComputeWarps / 4;
 constexpr int kTmemCols = 128;
-constexpr uint32_t kTmA = 0;              // scores: 32 columns, two interleaved halves
-constexpr uint32_t kTmOS = 32;            // outputs (lane offset 0) and state increment (lane offset 16)
+constexpr uint32_t kTmA = 0;              // scores: two buffers of 32 columns, each two interleaved halves
+constexpr uint32_t kTmOS = 64;            // outputs (lane offset 0) and state increment (lane offset 16)
+constexpr int kSlots = kNumStages;        // per-chunk exchange slots (chunk totals, exact-path flag), one per stage
 constexpr uint32_t kLane16 = 16u << 16;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kWideLimit = 64.f * kLog2e;   // largest in-chunk decay (log2 units) the tf32 path takes
@@ -107,9 +111,10 @@ constexpr int kAggStride = kD * kD + kD;
 
 // shared memory map (bytes from a 1024-aligned base)
 constexpr int kOffStage = 0;
-constexpr int kOffQbar = kNumStages * kStageBytes;       // 16 KB tf32 (two 8 KB halves)
-constexpr int kOffKbar = kOffQbar + 2 * kTileBytes;
-constexpr int kOffS16 = kOffKbar + 2 * kTileBytes;
+constexpr int kOffQbar = kNumStages * kStageBytes;       // two buffers of {qb 16 KB, kb 16 KB} tf32 (each two 8 KB halves)
+constexpr int kQkBufBytes = 4 * kTileBytes;
+constexpr int kOffKbarRel = 2 * kTileBytes;              // kb inside a buffer
+constexpr int kOffS16 = kOffQbar + 2 * kQkBufBytes;
 constexpr int kOffMisc = kOffS16 + kTileBytes;
 constexpr int kMiscBytes = 4096 + 512 * kComputeWarps;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + alignment slack
@@ -117,13 +122,15 @@ constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + alignment slack
 struct Misc {
     uint64_t full[kNumStages];
     uint64_t empty[kNumStages];
-    uint64_t ops_ready, a_done, a16_ready, os_done, acc_free, s16_ready;
+    // A barrier may run at most one phase ahead of its slowest waiter.  Barriers whose producer can run further
+    // ahead are rings indexed like the resource they guard (stage, or tf32 buffer / score accumulator).
+    uint64_t ops_ready[kNumStages], a_done[2], a_free[2], a16_ready[2], os_done, acc_free, s16_ready;
     uint32_t tmem_base;
     volatile uint32_t abort;
     int item;
-    uint32_t wide[2];
-    alignas(16) float tot[2][kComputeWarps][kD];   // per-warp gate sums of the two chunks in flight (float2 access)
-    alignas(16) float b4s[2][kD];      // chunk totals G_L per channel
+    uint32_t wide[kSlots];
+    alignas(16) float tot[2][kComputeWarps][kD];   // per-warp gate sums (float2 access), double-buffered
+    alignas(16) float b4s[kSlots][kD]; // chunk totals G_L per channel
     float ssq[kColSplit][kChunk];      // fused epilogue: per-row partial sums of squares
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "misc block too large");
@@ -267,12 +274,12 @@ template <bool kRev> __device__ __forceinline__ uint32_t off32(const GateLane& g
 // and chunks on the exact-score path (`wide`: G and raw q, k are stashed in plain layouts where the
 // tf32 operands would go).  Recomputes the running gate sum from the (still raw) gate tile.
 template <bool kRev>
-__device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, int valid, int w, int l, bool state_only,
-                                               bool wide, float off0, float off1, float b40, float b41, float e10,
+__device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, uint32_t qbar, int valid, int w, int l,
+                                               bool state_only, bool wide, float off0, float off1, float b40, float b41, float e10,
                                                float e11, float e20, float e21) {
     const GateLane gl = gate_lane<kRev>(w, l);
     const uint32_t tq = stage, tk = stage + kTileBytes, tg = stage + 2 * kTileBytes, tv = stage + 3 * kTileBytes;
-    const uint32_t qbar = c.smem + kOffQbar, kbar = c.smem + kOffKbar;
+    const uint32_t kbar = qbar + kOffKbarRel;
     const uint32_t c0 = 2u * l;
     float a0 = off0, a1 = off1;
 #pragma unroll 1
@@ -306,15 +313,15 @@ __device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, int
 }
 
 template <bool kStateOnly, bool kRev>
-__device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, int n, int valid, int w, int l) {
+__device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, uint32_t qbar, int n, int valid, int w, int l) {
     constexpr int R = kRowsPerThread;
     static_assert(R == 8 || R == 4, "the swizzle shortcut needs a row count that divides 8");
     const Params& P = *c.p;
     Misc& M = *c.misc;
-    const int par = n & 1;
+    const int par = n & 1, slot = n % kSlots;
     const GateLane gl = gate_lane<kRev>(w, l);
     const uint32_t tq = stage, tk = stage + kTileBytes, tg = stage + 2 * kTileBytes;
-    const uint32_t qbar = c.smem + kOffQbar, kbar = c.smem + kOffKbar;
+    const uint32_t kbar = qbar + kOffKbarRel;
     const uint32_t c0 = 2u * l;
     const uint32_t tot_sa = smem_u32(&M.tot[par][0][c0]);   // + ww * kD * 4
     const bool ragged = valid < kChunk;
@@ -361,19 +368,19 @@ __device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, int n,
         b40 += t.x;
         b41 += t.y;
     }
-    if (w == 0) sts64(smem_u32(&M.b4s[par][c0]), b40, b41);
+    if (w == 0) sts64(smem_u32(&M.b4s[slot][c0]), b40, b41);
     bool wide = false;
     float e10 = 0.f, e11 = 0.f, e20 = 0.f, e21 = 0.f;
     if (!kStateOnly) {
         wide = __any_sync(0xffffffffu, (-b40 > kWideLimit) || (-b41 > kWideLimit));
-        if (w == 0 && l == 0) M.wide[par] = wide ? 1u : 0u;
+        if (w == 0 && l == 0) M.wide[slot] = wide ? 1u : 0u;
         e10 = ex2(-gm0);
         e11 = ex2(-gm1);
         e20 = ex2(gm0 - b40);
         e21 = ex2(gm1 - b41);
     }
     if (ragged || wide) {
-        gate_rows_general<kRev>(c, stage, valid, w, l, kStateOnly, wide, off0, off1, b40, b41, e10, e11, e20, e21);
+        gate_rows_general<kRev>(c, stage, qbar, valid, w, l, kStateOnly, wide, off0, off1, b40, b41, e10, e11, e20, e21);
     } else {
         // straight-line: exponents first, then products, then stores
         const float ck0 = b40 - off0, ck1 = b41 - off1;
@@ -408,14 +415,14 @@ __device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, int n,
     GLA_EVC(c, 43);
 }
 
-__device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, int n, int valid, int w, int l,
+__device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, uint32_t qbar, int n, int valid, int w, int l,
                                           bool state_only) {
     if (c.p->rev) {
-        if (state_only) gate_math_t<true, true>(c, stage, n, valid, w, l);
-        else gate_math_t<false, true>(c, stage, n, valid, w, l);
+        if (state_only) gate_math_t<true, true>(c, stage, qbar, n, valid, w, l);
+        else gate_math_t<false, true>(c, stage, qbar, n, valid, w, l);
     } else {
-        if (state_only) gate_math_t<true, false>(c, stage, n, valid, w, l);
-        else gate_math_t<false, false>(c, stage, n, valid, w, l);
+        if (state_only) gate_math_t<true, false>(c, stage, qbar, n, valid, w, l);
+        else gate_math_t<false, false>(c, stage, qbar, n, valid, w, l);
     }
 }
 
@@ -425,10 +432,10 @@ __device__ __forceinline__ uint32_t sw_f16(uint32_t row, uint32_t col) {     // 
 
 // Exact intra-chunk scores for chunks whose gates are too strong for a common reference:
 // A[i][j] = sum_c q[i][c] k[j][c] 2^(G[i][c] - G[j][c]) for j at or before i along the scan.
-__device__ __noinline__ void exact_scores(const Ctx& c, uint8_t* a16_tile, int tid) {
+__device__ __noinline__ void exact_scores(const Ctx& c, uint8_t* a16_tile, const uint8_t* qkbuf, int tid) {
     const bool rev = c.p->rev != 0;
-    const uint8_t* gs = c.base + kOffQbar;
-    const uint8_t* qs = c.base + kOffKbar;
+    const uint8_t* gs = qkbuf;
+    const uint8_t* qs = qkbuf + kOffKbarRel;
     const uint8_t* ks = qs + kTileBytes;
     constexpr uint32_t kPerRow = kComputeThreads / kChunk;
     const uint32_t i = tid / kPerRow;
@@ -526,6 +533,13 @@ __device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
     return it;
 }
 
+// Warp roles (one CTA per SM):
+//   warps 0..7   gate group     raw q,k,g tiles -> qh, kh (fp16, in place) and qb, kb (tf32, two buffers)
+//   warps 8..15  epilogue group TMEM read-out: scores -> fp16 tile, outputs -> tile -> TMA store, state in fp32
+//                               registers, look-back and publication of segment states
+//   warp 16      TMA producer   warp 17  MMA issue
+// The gate group runs up to two chunks ahead of the epilogue group (bounded by the tf32 buffers), so operand
+// preparation of chunk i+1, i+2 overlaps the MMAs and epilogues of chunk i.
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params P) {
     extern __shared__ uint8_t smem_raw[];
@@ -539,6 +553,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
 #ifdef GLA_TRACE
     uint32_t trace_n = 0;
 #endif
+    constexpr int kWarpProducer = 2 * kComputeWarps, kWarpMma = 2 * kComputeWarps + 1;
 
     Ctx ctx;
     ctx.p = &P;
@@ -555,43 +570,35 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             mbar_init(smem_u32(&M.full[s]), 1);
             mbar_init(smem_u32(&M.empty[s]), 1);
         }
-        mbar_init(smem_u32(&M.ops_ready), kComputeThreads);
-        mbar_init(smem_u32(&M.a_done), 1);
-        mbar_init(smem_u32(&M.a16_ready), kComputeThreads);
+        for (int s = 0; s < kNumStages; ++s) mbar_init(smem_u32(&M.ops_ready[s]), kComputeThreads);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&M.a_done[b]), 1);
+            mbar_init(smem_u32(&M.a_free[b]), kComputeThreads);
+            mbar_init(smem_u32(&M.a16_ready[b]), kComputeThreads);
+        }
         mbar_init(smem_u32(&M.os_done), 1);
         mbar_init(smem_u32(&M.acc_free), kComputeThreads);
         mbar_init(smem_u32(&M.s16_ready), kComputeThreads);
         M.abort = 0;
         fence_mbar_init();
     }
-    if (w == kComputeWarps) {
+    if (w == kWarpProducer) {
         tmem_alloc(smem_u32(&M.tmem_base), kTmemCols);
         tmem_relinquish();
     }
-    if (w == kComputeWarps + 1 && l == 0) {
-        for (int t = 0; t < kNumTensors; ++t)
-            if (t != TGATE || P.gated)
-                tma_prefetch_desc(&maps.m[t][0]);
+    if (w == kWarpMma && l == 0) {
+        for (int t = 0; t < TGATE; ++t) tma_prefetch_desc(&maps.m[t][0]);
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = M.tmem_base;
 
-    // use counters of every barrier, kept per role (all roles see the same sequence of uses)
-    uint32_t n_full[kNumStages] = {}, n_empty[kNumStages] = {};
-    uint32_t n_ops = 0, n_adone = 0, n_a16 = 0, n_osdone = 0, n_accfree = 0, n_s16 = 0;
-    uint32_t chunk_ctr = 0;   // chunks processed by this CTA so far: stage = ctr % 2, parity slot = ctr & 1
-
-    // State ownership: lanes 16-31 of compute warp w hold, in fp32, columns [kSc*ch, kSc*ch+kSc) of
-    // state row (channel) my_c = 16*(w&3) + (l&15), ch = w>>2.
-    constexpr int kSc = kD / kColSplit;       // O / state columns per thread
-    constexpr int kAc = 32 / kColSplit;       // score columns per thread (per 32-column half)
-    float S[kSc];
-    const bool owner = (w < kComputeWarps) && (l >= 16);
-    const int quad = w & 3, ch = (w >> 2) % kColSplit;
-    const int my_c = 16 * quad + (l & 15);
-    const int col0 = kSc * ch;                // first O / state column of this thread
+    // Every role walks the same sequence of chunks and keeps its own counters:
+    //   ctr  chunks seen so far (both passes): stage = ctr % kNumStages, exchange slot = ctr % kSlots
+    //   c2   output-pass chunks seen so far: tf32 buffer / score accumulator = c2 & 1
+    uint32_t ctr = 0, c2 = 0;
+    uint32_t n_s16 = 0, n_accfree = 0, n_osdone = 0;   // single barriers: use counts (MMA / epilogue roles)
 
     while (true) {
         if (tid == 0) M.item = static_cast<int>(atomicAdd(P.ctrl, 1u));
@@ -601,15 +608,14 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         const ItemInfo it = decode_item(P, item);
         const int npass = it.state_pass ? 2 : 1;
 
-        if (w == kComputeWarps) {
+        if (w == kWarpProducer) {
             // ------------------------------------------------------------ TMA producer
             if (l == 0) {
-                uint32_t ctr = chunk_ctr;
                 for (int pass = 0; pass < npass; ++pass) {
                     const bool state_only = it.state_pass && pass == 0;
                     for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                        const uint32_t s = ctr % kNumStages;
-                        mbar_wait(ctx, &M.empty[s], (n_empty[s]++ & 1u) ^ 1u);
+                        const uint32_t s = ctr % kNumStages, n = ctr / kNumStages;
+                        mbar_wait(ctx, &M.empty[s], (n & 1u) ^ 1u);
                         GLA_EV(30);
                         const int p0 = (it.first_chunk + i) * kChunk;
                         const int valid = chunk_valid(p0, P.T);
@@ -629,40 +635,50 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                 }
             }
             __syncwarp();
-        } else if (w == kComputeWarps + 1) {
+        } else if (w == kWarpMma) {
             // ------------------------------------------------------------ MMA issue
             if (l == 0) {
                 constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 32);
                 constexpr uint32_t idO = umma_idesc(FMT_F16, 0, 1, 64, 64);
                 constexpr uint32_t idS = umma_idesc(FMT_F16, 1, 1, 64, 64);
-                // descriptors differ only in their 14-bit start-address field: add byte offsets >> 4
-                const uint64_t dQbar = umma_desc_sw128(base + kOffQbar), dKbar = umma_desc_sw128(base + kOffKbar);
+                const uint32_t tmO = tmem + kTmOS, tmS = tmem + kTmOS + kLane16;
                 const uint64_t dS16 = umma_desc_sw128(base + kOffS16, 8192);
-                const uint32_t tmA = tmem + kTmA, tmO = tmem + kTmOS, tmS = tmem + kTmOS + kLane16;
-                uint32_t ctr = chunk_ctr;
+                // score MMA of the output-pass chunk with running indices (cc, k2): waits for its operands
+                auto issue_scores = [&](uint32_t cc, uint32_t k2) {
+                    const uint32_t s = cc % kNumStages, b = k2 & 1u;
+                    mbar_wait(ctx, &M.full[s], (cc / kNumStages) & 1u);
+                    mbar_wait(ctx, &M.ops_ready[s], (cc / kNumStages) & 1u);
+                    mbar_wait(ctx, &M.a_free[b], ((k2 >> 1) & 1u) ^ 1u);   // epilogue done with this buffer's previous use
+                    GLA_EV(20);
+                    tc_fence_after();
+                    if (!M.wide[cc % kSlots]) {
+                        const uint64_t dQ = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes);
+                        const uint64_t dK = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes + kOffKbarRel);
+                        const uint32_t tmA = tmem + kTmA + 32u * b;
+#pragma unroll
+                        for (uint32_t ks = 0; ks < 8; ++ks) {
+                            const uint32_t o = ((ks >> 2) * kTileBytes + (ks & 3) * 32u) >> 4;
+                            umma_tf32(tmA, dQ + o, dK + o, idA, ks);
+                            umma_tf32(tmA + kLane16, dQ + o, dK + o + ((32 * 128) >> 4), idA, ks);
+                        }
+                    }
+                    umma_commit(smem_u32(&M.a_done[b]));
+                    GLA_EV(21);
+                };
                 for (int pass = 0; pass < npass; ++pass) {
                     const bool state_only = it.state_pass && pass == 0;
+                    if (!state_only) issue_scores(ctr, c2);
                     for (int i = 0; i < it.nchunks; ++i, ++ctr) {
                         const uint32_t s = ctr % kNumStages;
                         const uint32_t stage = base + kOffStage + s * kStageBytes;
                         const uint64_t dq = umma_desc_sw128(stage), dk = umma_desc_sw128(stage + kTileBytes, 8192),
                                        da16 = umma_desc_sw128(stage + 2 * kTileBytes),
                                        dv = umma_desc_sw128(stage + 3 * kTileBytes, 8192);
-                        mbar_wait(ctx, &M.full[s], n_full[s]++ & 1u);
-                        mbar_wait(ctx, &M.ops_ready, n_ops++ & 1u);
-                        GLA_EV(20);
-                        tc_fence_after();
-                        if (!state_only) {
-                            if (!M.wide[ctr & 1]) {
-#pragma unroll
-                                for (uint32_t ks = 0; ks < 8; ++ks) {
-                                    const uint32_t o = ((ks >> 2) * kTileBytes + (ks & 3) * 32u) >> 4;
-                                    umma_tf32(tmA, dQbar + o, dKbar + o, idA, ks);
-                                    umma_tf32(tmA + kLane16, dQbar + o, dKbar + o + ((32 * 128) >> 4), idA, ks);
-                                }
-                            }
-                            umma_commit(smem_u32(&M.a_done));
-                            GLA_EV(21);
+                        if (state_only) {
+                            mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);
+                            mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);
+                        } else {
+                            if (i + 1 < it.nchunks) issue_scores(ctr + 1, c2 + 1);   // runs ahead of the epilogues
                             mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
                         }
                         // both accumulators of the O/S columns must have been read by the epilogue
@@ -671,30 +687,59 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         tc_fence_after();
                         if (!state_only) {
 #pragma unroll
-                            for (uint32_t ks = 0; ks < 4; ++ks)
-                                umma_f16(tmO, dq + ks * 2u, dS16 + ks * 128u, idO, ks);
-                            mbar_wait(ctx, &M.a16_ready, n_a16++ & 1u);
+                            for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmO, dq + ks * 2u, dS16 + ks * 128u, idO, ks);
+                            mbar_wait(ctx, &M.a16_ready[c2 & 1u], (c2 >> 1) & 1u);
                             GLA_EV(23);
                             tc_fence_after();
 #pragma unroll
-                            for (uint32_t ks = 0; ks < 4; ++ks)
-                                umma_f16(tmO, da16 + ks * 2u, dv + ks * 128u, idO, 1);
+                            for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmO, da16 + ks * 2u, dv + ks * 128u, idO, 1);
+                            ++c2;
                         }
 #pragma unroll
-                        for (uint32_t ks = 0; ks < 4; ++ks)
-                            umma_f16(tmS, dk + ks * 128u, dv + ks * 128u, idS, ks);
+                        for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmS, dk + ks * 128u, dv + ks * 128u, idS, ks);
                         umma_commit(smem_u32(&M.os_done));
                         GLA_EV(24);
                     }
                 }
             }
             __syncwarp();
+        } else if (w < kComputeWarps) {
+            // ------------------------------------------------------------ gate group
+            for (int pass = 0; pass < npass; ++pass) {
+                const bool state_only = it.state_pass && pass == 0;
+                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                    const uint32_t s = ctr % kNumStages;
+                    mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);
+                    uint32_t qbar = 0;
+                    if (!state_only) {
+                        const uint32_t b = c2 & 1u;
+                        mbar_wait(ctx, &M.a_free[b], ((c2 >> 1) & 1u) ^ 1u);   // buffer's previous scores consumed
+                        qbar = base + kOffQbar + b * kQkBufBytes;
+                        ++c2;
+                    }
+                    GLA_EV(12);
+                    gate_math(ctx, base + kOffStage + s * kStageBytes, qbar, static_cast<int>(ctr),
+                              chunk_valid((it.first_chunk + i) * kChunk, P.T), w, l, state_only);
+                    mbar_arrive(smem_u32(&M.ops_ready[s]));
+                    GLA_EV(13);
+                }
+            }
         } else {
-            // ------------------------------------------------------------ compute warps
+            // ------------------------------------------------------------ epilogue group
+            // State ownership: lanes 16-31 of epilogue warp e hold, in fp32, columns [kSc*ch, kSc*ch+kSc) of
+            // state row (channel) my_c = 16*(e&3) + (l&15), ch = e>>2; lanes 0-15 hold the same columns of
+            // output row 16*(e&3) + l.
+            constexpr int kSc = kD / kColSplit;       // O / state columns per thread
+            constexpr int kAc = 32 / kColSplit;       // score columns per thread (per 32-column half)
+            const int e = w - kComputeWarps, etid = tid - kComputeThreads;
+            const bool owner = l >= 16;
+            const int quad = e & 3, ch = e >> 2;
+            const int my_c = 16 * quad + (l & 15);
+            const int col0 = kSc * ch;
+            const uint32_t rho = 16 * quad + (l & 15);
             const size_t srow = (static_cast<size_t>(it.seq) * kD + my_c) * kD + col0;   // this thread's part of a state row
             const size_t slot = static_cast<size_t>(it.seq) * P.NS + it.seg;
-            const uint32_t rho = 16 * quad + (l & 15);   // O row (lanes 0-15) or state row (lanes 16-31)
-            uint32_t ctr = chunk_ctr;
+            float S[kSc];
             float gsum = 0.f;       // log2 of the segment's total decay for channel my_c
 
             auto load_initial = [&]() {
@@ -717,8 +762,36 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
                 }
                 __threadfence();
-                named_bar_sync(1, kComputeThreads);
-                if (tid == 0) st_release_gpu(P.flags + slot, flag_value);
+                named_bar_sync(2, kComputeThreads);
+                if (etid == 0) st_release_gpu(P.flags + slot, flag_value);
+            };
+            // scores of the output-pass chunk with running indices (cc, k2): TMEM -> causal mask -> fp16 tile
+            // (takes the place of the raw gate tile of its stage)
+            auto scores = [&](uint32_t cc, uint32_t k2) {
+                const uint32_t s = cc % kNumStages, b = k2 & 1u;
+                const uint32_t a16 = base + kOffStage + s * kStageBytes + 2 * kTileBytes;
+                mbar_wait(ctx, &M.a_done[b], (k2 >> 1) & 1u);
+                GLA_EV(10);
+                tc_fence_after();
+                if (!M.wide[cc % kSlots]) {
+                    float x[kAc];
+                    tmem_row<kAc>(tmem, quad, kTmA + 32u * b + kAc * ch, x);
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&M.a_free[b]));
+                    const uint32_t j0 = (l >> 4) * 32u + kAc * ch;   // lanes 16-31 hold key rows 32-63
+#pragma unroll
+                    for (uint32_t j = 0; j < kAc; ++j) {
+                        const bool keep = P.rev ? (j0 + j >= rho) : (j0 + j <= rho);
+                        x[j] = keep ? x[j] : 0.f;
+                    }
+                    store_row_f16<kAc / 8>(a16, rho, j0 >> 3, x);
+                } else {
+                    exact_scores(ctx, base_ptr + (a16 - base), base_ptr + kOffQbar + b * kQkBufBytes, etid);
+                    mbar_arrive(smem_u32(&M.a_free[b]));
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(smem_u32(&M.a16_ready[b]));
+                GLA_EV(11);
             };
 
             for (int pass = 0; pass < npass; ++pass) {
@@ -788,129 +861,95 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                                 }
                             }
                             __threadfence();
-                            named_bar_sync(1, kComputeThreads);
-                            if (tid == 0) st_release_gpu(P.flags + slot, 2u);
+                            named_bar_sync(2, kComputeThreads);
+                            if (etid == 0) st_release_gpu(P.flags + slot, 2u);
                         }
                     }
                     if (owner) store_row_f16<kSc / 8>(base + kOffS16, rho, col0 >> 3, S);
                     fence_proxy_async_smem();
                     mbar_arrive(smem_u32(&M.s16_ready));
+                    scores(ctr, c2);
                 }
 
-                // software pipeline over the chunks: scores(i) | gate math(i+1) | outputs+state(i)
-                for (int i = -1; i < it.nchunks; ++i) {
-                    const uint32_t cc = ctr + static_cast<uint32_t>(i);       // running index of chunk i
-                    const uint32_t s = cc % kNumStages;
+                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                    const uint32_t s = ctr % kNumStages;
                     const uint32_t stage = base + kOffStage + s * kStageBytes;
-                    if (i >= 0 && !state_only) {
-                        // scores: TMEM -> causal mask -> fp16 tile (takes the place of the raw gate tile)
-                        mbar_wait(ctx, &M.a_done, n_adone++ & 1u);
-                        GLA_EV(10);
-                        tc_fence_after();
-                        if (!M.wide[cc & 1]) {
-                            float x[kAc];
-                            tmem_row<kAc>(tmem, quad, kTmA + kAc * ch, x);
-                            const uint32_t j0 = (l >> 4) * 32u + kAc * ch;   // lanes 16-31 hold key rows 32-63
-#pragma unroll
-                            for (uint32_t j = 0; j < kAc; ++j) {
-                                const bool keep = P.rev ? (j0 + j >= rho) : (j0 + j <= rho);
-                                x[j] = keep ? x[j] : 0.f;
-                            }
-                            store_row_f16<kAc / 8>(stage + 2 * kTileBytes, rho, j0 >> 3, x);
-                        } else {
-                            named_bar_sync(1, kComputeThreads);
-                            exact_scores(ctx, base_ptr + kOffStage + s * kStageBytes + 2 * kTileBytes, tid);
-                        }
-                        fence_proxy_async_smem();
-                        tc_fence_before();
-                        mbar_arrive(smem_u32(&M.a16_ready));
-                        GLA_EV(11);
+                    if (!state_only) {
+                        if (i + 1 < it.nchunks) scores(ctr + 1, c2 + 1);   // overlaps the output/state MMAs of chunk i
+                        ++c2;
                     }
-                    if (i + 1 < it.nchunks) {
-                        const uint32_t s1 = (cc + 1) % kNumStages;
-                        mbar_wait(ctx, &M.full[s1], n_full[s1]++ & 1u);
-                        GLA_EV(12);
-                        gate_math(ctx, base + kOffStage + s1 * kStageBytes, static_cast<int>(cc + 1),
-                                  chunk_valid((it.first_chunk + i + 1) * kChunk, P.T), w, l, state_only);
-                        if (!state_only) mbar_arrive(smem_u32(&M.ops_ready));
-                        GLA_EV(13);
+                    // lanes 0-15: outputs -> scale -> fp16 tile (takes the place of qh) -> TMA store
+                    // lanes 16-31: S <- 2^(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
+                    mbar_wait(ctx, &M.os_done, n_osdone++ & 1u);
+                    GLA_EV(14);
+                    tc_fence_after();
+                    float x[kSc];
+                    tmem_row<kSc>(tmem, quad, kTmOS + col0, x);
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&M.acc_free));
+                    const float b4 = ld_shared_f(smem_u32(&M.b4s[ctr % kSlots][my_c]));
+                    const float dec = owner ? ex2(b4) : 0.f;
+                    const float mul = owner ? 1.f : P.scale;
+                    if (owner) gsum += b4;
+#pragma unroll
+                    for (int v = 0; v < kSc; ++v) {
+                        S[v] = fmaf(dec, S[v], x[v]);
+                        x[v] = S[v] * mul;
                     }
-                    if (i >= 0) {
-                        // lanes 0-15: outputs -> scale -> fp16 tile (takes the place of qh) -> TMA store
-                        // lanes 16-31: S <- 2^(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
-                        mbar_wait(ctx, &M.os_done, n_osdone++ & 1u);
-                        GLA_EV(14);
-                        tc_fence_after();
-                        float x[kSc];
-                        tmem_row<kSc>(tmem, quad, kTmOS + col0, x);
-                        tc_fence_before();
-                        mbar_arrive(smem_u32(&M.acc_free));
-                        const float b4 = ld_shared_f(smem_u32(&M.b4s[cc & 1][my_c]));
-                        const float dec = owner ? ex2(b4) : 0.f;
-                        const float mul = owner ? 1.f : P.scale;
-                        if (owner) gsum += b4;
+                    if (!state_only && P.gated) {
+                        // y = o * rsqrt(mean(o^2) + eps) * w * silu(gate); a row's 64 columns are split over
+                        // kColSplit warps, which exchange their partial sums of squares through shared memory
+                        float ss = 0.f;
 #pragma unroll
-                        for (int v = 0; v < kSc; ++v) {
-                            S[v] = fmaf(dec, S[v], x[v]);
-                            x[v] = S[v] * mul;
-                        }
-                        if (!state_only && P.gated) {
-                            // y = o * rsqrt(mean(o^2) + eps) * w * silu(gate); a row's 64 columns are split over
-                            // kColSplit warps, which exchange their partial sums of squares through shared memory
-                            float ss = 0.f;
+                        for (int v = 0; v < kSc; ++v) ss = fmaf(x[v], x[v], ss);
+                        if (!owner) M.ssq[ch][rho] = ss;
+                        named_bar_sync(2, kComputeThreads);
+                        if (!owner) {
+                            float tot = 0.f;
 #pragma unroll
-                            for (int v = 0; v < kSc; ++v) ss = fmaf(x[v], x[v], ss);
-                            if (!owner) M.ssq[ch][rho] = ss;
-                            named_bar_sync(1, kComputeThreads);
-                            if (!owner) {
-                                float tot = 0.f;
+                            for (int cc2 = 0; cc2 < kColSplit; ++cc2) tot += M.ssq[cc2][rho];
+                            const float rinv = rsqrtf(tot * (1.f / kD) + P.rms_eps);
+                            // token read at this row of the chunk (same mapping as the TMA boxes)
+                            const int p0 = (it.first_chunk + i) * kChunk;
+                            const int u = (P.rev ? (P.T - p0 - kChunk) : p0) + static_cast<int>(rho);
+                            if (u >= 0 && u < P.T) {
+                                const int cc3 = u / P.Hc, rr = u - cc3 * P.Hc;
+                                const long long tok = (P.Wc > 1) ? static_cast<long long>(rr) * P.Wc + cc3 : u;
+                                const uint4* gp = reinterpret_cast<const uint4*>(
+                                    P.gate + it.b * P.gate_sb + tok * P.gate_st + it.h * P.gate_sh + col0);
+                                const uint4* wp = reinterpret_cast<const uint4*>(P.rms_w + col0);
 #pragma unroll
-                                for (int cc2 = 0; cc2 < kColSplit; ++cc2) tot += M.ssq[cc2][rho];
-                                const float rinv = rsqrtf(tot * (1.f / kD) + P.rms_eps);
-                                // token read at this row of the chunk (same mapping as the TMA boxes)
-                                const int p0 = (it.first_chunk + i) * kChunk;
-                                const int u = (P.rev ? (P.T - p0 - kChunk) : p0) + static_cast<int>(rho);
-                                if (u >= 0 && u < P.T) {
-                                    const int cc3 = u / P.Hc, rr = u - cc3 * P.Hc;
-                                    const long long tok = (P.Wc > 1) ? static_cast<long long>(rr) * P.Wc + cc3 : u;
-                                    const uint4* gp = reinterpret_cast<const uint4*>(
-                                        P.gate + it.b * P.gate_sb + tok * P.gate_st + it.h * P.gate_sh + col0);
-                                    const uint4* wp = reinterpret_cast<const uint4*>(P.rms_w + col0);
+                                for (int v8 = 0; v8 < kSc / 8; ++v8) {
+                                    const uint4 g4 = __ldg(gp + v8), w4 = __ldg(wp + v8);
+                                    const uint32_t gu[4] = {g4.x, g4.y, g4.z, g4.w}, wu[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
-                                    for (int v8 = 0; v8 < kSc / 8; ++v8) {
-                                        const uint4 g4 = __ldg(gp + v8), w4 = __ldg(wp + v8);
-                                        const uint32_t gu[4] = {g4.x, g4.y, g4.z, g4.w}, wu[4] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-                                        for (int q2 = 0; q2 < 4; ++q2) {
-                                            const float2 gf = unpack_half2(gu[q2]), wf = unpack_half2(wu[q2]);
-                                            x[8 * v8 + 2 * q2] *= rinv * wf.x * (gf.x / (1.f + __expf(-gf.x)));
-                                            x[8 * v8 + 2 * q2 + 1] *= rinv * wf.y * (gf.y / (1.f + __expf(-gf.y)));
-                                        }
+                                    for (int q2 = 0; q2 < 4; ++q2) {
+                                        const float2 gf = unpack_half2(gu[q2]), wf = unpack_half2(wu[q2]);
+                                        x[8 * v8 + 2 * q2] *= rinv * wf.x * (gf.x / (1.f + __expf(-gf.x)));
+                                        x[8 * v8 + 2 * q2 + 1] *= rinv * wf.y * (gf.y / (1.f + __expf(-gf.y)));
                                     }
                                 }
                             }
                         }
-                        if (!state_only) {
-                            store_row_f16<kSc / 8>(owner ? base + kOffS16 : stage, rho, col0 >> 3, x);
-                            fence_proxy_async_smem();
-                            if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.s16_ready));
-                            GLA_EV(15);
-                            named_bar_sync(1, kComputeThreads);
-                            if (tid == 0) {
-                                const int p0 = (it.first_chunk + i) * kChunk;
-                                for_each_box(p0, P.T, P.Hc, P.rev, [&](int id, int r, int c, int row) {
-                                    tma_store_5d(&maps.m[TO][id], stage + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
-                                });
-                                tma_store_commit();
-                                tma_store_wait_read();
-                            }
-                        }
-                        if (tid == 0) mbar_arrive(smem_u32(&M.empty[s]));
-                        GLA_EV(16);
                     }
-                    if (state_only && i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.ops_ready));
+                    if (!state_only) {
+                        store_row_f16<kSc / 8>(owner ? base + kOffS16 : stage, rho, col0 >> 3, x);
+                        fence_proxy_async_smem();
+                        if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.s16_ready));
+                        GLA_EV(15);
+                        named_bar_sync(2, kComputeThreads);
+                        if (etid == 0) {
+                            const int p0 = (it.first_chunk + i) * kChunk;
+                            for_each_box(p0, P.T, P.Hc, P.rev, [&](int id, int r, int c, int row) {
+                                tma_store_5d(&maps.m[TO][id], stage + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
+                            });
+                            tma_store_commit();
+                            tma_store_wait_read();
+                        }
+                    }
+                    if (etid == 0) mbar_arrive(smem_u32(&M.empty[s]));
+                    GLA_EV(16);
                 }
-                ctr += static_cast<uint32_t>(it.nchunks);
 
                 if (state_only) {
                     if (it.seg == 0) {
@@ -928,14 +967,13 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
             }
         }
-        chunk_ctr += static_cast<uint32_t>(npass * it.nchunks);
         __syncthreads();   // the item is drained: every role restarts from the same counters
     }
 
-    if (tid == 0) tma_store_wait_all();
+    if (tid == kComputeThreads) tma_store_wait_all();
     tc_fence_before();
     __syncthreads();
-    if (w == kComputeWarps) tmem_dealloc(tmem, kTmemCols);
+    if (w == kWarpProducer) tmem_dealloc(tmem, kTmemCols);
 }
 
 }  // namespace gla
