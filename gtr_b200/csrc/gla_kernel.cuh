@@ -54,7 +54,7 @@ constexpr int kNumStages = GLA_STAGES;
 // split its columns.
 constexpr int kComputeWarps = GLA_COMPUTE_WARPS;
 constexpr int kComputeThreads = 32 * kComputeWarps;
-constexpr int kThreads = 2 * kComputeThreads + 64;
+constexpr int kThreads = 2 * kComputeThreads + 96;   // + TMA producer, score-MMA issuer, output/state-MMA issuer
 constexpr int kRowsPerThread = kChunk / kComputeWarps;   // gate math: logical rows per thread
 constexpr int kColSplit = kComputeWarps / 4;
 constexpr int kTmemCols = 128;
@@ -147,7 +147,7 @@ struct Ctx {
     uint32_t* trace_n;
 #endif
 };
-#ifdef GLA_TRACE
+#if defined(GLA_TRACE) && defined(GLA_TRACE_FINE)
 #define GLA_EVC(c, id) do { if (blockIdx.x == 0 && !((c).p->dbg & 128) && (threadIdx.x & 31) == 0 && *(c).trace_n < 4096u) { \
         (c).p->trace[(threadIdx.x >> 5) * 4096u + (*(c).trace_n)++] = ((unsigned long long)clock64() << 8) | (unsigned long long)(id); } } while (0)
 #else
@@ -537,7 +537,9 @@ __device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
 //   warps 0..7   gate group     raw q,k,g tiles -> qh, kh (fp16, in place) and qb, kb (tf32, two buffers)
 //   warps 8..15  epilogue group TMEM read-out: scores -> fp16 tile, outputs -> tile -> TMA store, state in fp32
 //                               registers, look-back and publication of segment states
-//   warp 16      TMA producer   warp 17  MMA issue
+//   warp 16      TMA producer   warp 17  score MMAs   warp 18  output and state MMAs
+// (one thread needs ~100 cycles to issue a tcgen05.mma whatever its shape, so the 28 small MMAs of a chunk
+// are issued from two threads)
 // The gate group runs up to two chunks ahead of the epilogue group (bounded by the tf32 buffers), so operand
 // preparation of chunk i+1, i+2 overlaps the MMAs and epilogues of chunk i.
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
@@ -636,51 +638,56 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             }
             __syncwarp();
         } else if (w == kWarpMma) {
-            // ------------------------------------------------------------ MMA issue
+            // ------------------------------------------------------------ score MMAs (output pass only)
             if (l == 0) {
                 constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 32);
+                for (int pass = 0; pass < npass; ++pass) {
+                    const bool state_only = it.state_pass && pass == 0;
+                    for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                        const uint32_t s = ctr % kNumStages, b = c2 & 1u;
+                        // a parity wait only tells apart consecutive phases, so this thread has to observe
+                        // every phase of the ring, also those of state-only chunks it has nothing to do for
+                        mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);
+                        if (state_only) continue;
+                        mbar_wait(ctx, &M.a_free[b], ((c2 >> 1) & 1u) ^ 1u);   // epilogue done with this buffer's previous use
+                        GLA_EV(20);
+                        tc_fence_after();
+                        if (!M.wide[ctr % kSlots]) {
+                            const uint64_t dQ = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes);
+                            const uint64_t dK = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes + kOffKbarRel);
+                            const uint32_t tmA = tmem + kTmA + 32u * b;
+#pragma unroll
+                            for (uint32_t ks = 0; ks < 8; ++ks) {
+                                const uint32_t o = ((ks >> 2) * kTileBytes + (ks & 3) * 32u) >> 4;
+                                umma_tf32(tmA, dQ + o, dK + o, idA, ks);
+                                umma_tf32(tmA + kLane16, dQ + o, dK + o + ((32 * 128) >> 4), idA, ks);
+                            }
+                        }
+                        umma_commit(smem_u32(&M.a_done[b]));
+                        GLA_EV(21);
+                        ++c2;
+                    }
+                }
+            }
+            __syncwarp();
+        } else if (w == kWarpMma + 1) {
+            // ------------------------------------------------------------ output and state MMAs
+            if (l == 0) {
                 constexpr uint32_t idO = umma_idesc(FMT_F16, 0, 1, 64, 64);
                 constexpr uint32_t idS = umma_idesc(FMT_F16, 1, 1, 64, 64);
                 const uint32_t tmO = tmem + kTmOS, tmS = tmem + kTmOS + kLane16;
                 const uint64_t dS16 = umma_desc_sw128(base + kOffS16, 8192);
-                // score MMA of the output-pass chunk with running indices (cc, k2): waits for its operands
-                auto issue_scores = [&](uint32_t cc, uint32_t k2) {
-                    const uint32_t s = cc % kNumStages, b = k2 & 1u;
-                    mbar_wait(ctx, &M.full[s], (cc / kNumStages) & 1u);
-                    mbar_wait(ctx, &M.ops_ready[s], (cc / kNumStages) & 1u);
-                    mbar_wait(ctx, &M.a_free[b], ((k2 >> 1) & 1u) ^ 1u);   // epilogue done with this buffer's previous use
-                    GLA_EV(20);
-                    tc_fence_after();
-                    if (!M.wide[cc % kSlots]) {
-                        const uint64_t dQ = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes);
-                        const uint64_t dK = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes + kOffKbarRel);
-                        const uint32_t tmA = tmem + kTmA + 32u * b;
-#pragma unroll
-                        for (uint32_t ks = 0; ks < 8; ++ks) {
-                            const uint32_t o = ((ks >> 2) * kTileBytes + (ks & 3) * 32u) >> 4;
-                            umma_tf32(tmA, dQ + o, dK + o, idA, ks);
-                            umma_tf32(tmA + kLane16, dQ + o, dK + o + ((32 * 128) >> 4), idA, ks);
-                        }
-                    }
-                    umma_commit(smem_u32(&M.a_done[b]));
-                    GLA_EV(21);
-                };
                 for (int pass = 0; pass < npass; ++pass) {
                     const bool state_only = it.state_pass && pass == 0;
-                    if (!state_only) issue_scores(ctr, c2);
                     for (int i = 0; i < it.nchunks; ++i, ++ctr) {
                         const uint32_t s = ctr % kNumStages;
                         const uint32_t stage = base + kOffStage + s * kStageBytes;
                         const uint64_t dq = umma_desc_sw128(stage), dk = umma_desc_sw128(stage + kTileBytes, 8192),
                                        da16 = umma_desc_sw128(stage + 2 * kTileBytes),
                                        dv = umma_desc_sw128(stage + 3 * kTileBytes, 8192);
-                        if (state_only) {
-                            mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);
-                            mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);
-                        } else {
-                            if (i + 1 < it.nchunks) issue_scores(ctr + 1, c2 + 1);   // runs ahead of the epilogues
-                            mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
-                        }
+                        mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);          // v arrives by TMA
+                        mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);     // qh, kh written in place
+                        if (!state_only) mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
                         // both accumulators of the O/S columns must have been read by the epilogue
                         mbar_wait(ctx, &M.acc_free, (n_accfree++ & 1u) ^ 1u);
                         GLA_EV(22);
