@@ -178,7 +178,15 @@ __device__ __forceinline__ float ex2(float x) {   // 2^x, one MUFU op; results b
 __device__ __forceinline__ float round_tf32(float x) {
     return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
-// two floats -> packed fp16 pair, round to nearest, saturating to the largest finite value
+// two floats -> packed fp16 pair, round to nearest.  One instruction; values beyond the fp16 range
+// become infinities, as with the reference kernels' conversions (a saturating conversion costs
+// several extra integer instructions per pair, too many for the per-element hot loops).
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// saturating variant for cold paths
 __device__ __forceinline__ uint32_t pack_half2_sat(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

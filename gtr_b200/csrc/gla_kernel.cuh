@@ -345,14 +345,25 @@ __device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, uint32
     float cs0[R], cs1[R];
     {
         float a0 = 0.f, a1 = 0.f;
+        if (!ragged) {
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const float2 gv = unpack_half2(graw[i]);
-            const bool live = !ragged || R * w + i < valid;
-            a0 += live ? gv.x * kLog2e : 0.f;
-            a1 += live ? gv.y * kLog2e : 0.f;
-            cs0[i] = a0;
-            cs1[i] = a1;
+            for (int i = 0; i < R; ++i) {
+                const float2 gv = unpack_half2(graw[i]);
+                a0 = fmaf(gv.x, kLog2e, a0);
+                a1 = fmaf(gv.y, kLog2e, a1);
+                cs0[i] = a0;
+                cs1[i] = a1;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                const float2 gv = unpack_half2(graw[i]);
+                const bool live = R * w + i < valid;
+                a0 += live ? gv.x * kLog2e : 0.f;
+                a1 += live ? gv.y * kLog2e : 0.f;
+                cs0[i] = a0;
+                cs1[i] = a1;
+            }
         }
         sts64(tot_sa + w * kD * 4, a0, a1);
     }
@@ -398,11 +409,11 @@ __device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, uint32
         for (int i = 0; i < R; ++i) {
             const float2 kv = unpack_half2(kraw[i]);
             const float kh0 = kv.x * ek0[i], kh1 = kv.y * ek1[i];
-            sts32(tk + off16<kRev>(gl, i), pack_half2_sat(kh0, kh1));
+            sts32(tk + off16<kRev>(gl, i), pack_half2(kh0, kh1));
             if (!kStateOnly) {
                 const float2 qv = unpack_half2(qraw[i]);
                 const float qh0 = qv.x * eq0[i], qh1 = qv.y * eq1[i];
-                sts32(tq + off16<kRev>(gl, i), pack_half2_sat(qh0, qh1));
+                sts32(tq + off16<kRev>(gl, i), pack_half2(qh0, qh1));
                 if (!GLA_DBG(1)) {
                     sts64(qbar + off32<kRev>(gl, i), round_tf32(qh0 * e10), round_tf32(qh1 * e11));
                     sts64(kbar + off32<kRev>(gl, i), round_tf32(kh0 * e20), round_tf32(kh1 * e21));
@@ -478,8 +489,8 @@ __device__ __forceinline__ void store_row_f16(uint32_t tile, uint32_t row, uint3
 #pragma unroll
     for (uint32_t m = 0; m < N8; ++m) {
         const uint32_t a = tile + row * 128u + ((((unit0 + m) ^ row) & 7u) << 4);
-        st_shared_v4(a, pack_half2_sat(x[8 * m], x[8 * m + 1]), pack_half2_sat(x[8 * m + 2], x[8 * m + 3]),
-                     pack_half2_sat(x[8 * m + 4], x[8 * m + 5]), pack_half2_sat(x[8 * m + 6], x[8 * m + 7]));
+        st_shared_v4(a, pack_half2(x[8 * m], x[8 * m + 1]), pack_half2(x[8 * m + 2], x[8 * m + 3]),
+                     pack_half2(x[8 * m + 4], x[8 * m + 5]), pack_half2(x[8 * m + 6], x[8 * m + 7]));
     }
 }
 
@@ -786,10 +797,20 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     tc_fence_before();
                     mbar_arrive(smem_u32(&M.a_free[b]));
                     const uint32_t j0 = (l >> 4) * 32u + kAc * ch;   // lanes 16-31 hold key rows 32-63
+                    // the block of 16 query rows (this quadrant) x kAc key columns lies before, on or after
+                    // the diagonal as a whole; only the diagonal block needs a per-element mask
+                    const uint32_t r0 = 16u * quad;
+                    const bool all_keep = P.rev ? (j0 >= r0 + 15u) : (j0 + kAc - 1u <= r0);
+                    const bool none = P.rev ? (j0 + kAc - 1u < r0) : (j0 > r0 + 15u);
+                    if (none) {
 #pragma unroll
-                    for (uint32_t j = 0; j < kAc; ++j) {
-                        const bool keep = P.rev ? (j0 + j >= rho) : (j0 + j <= rho);
-                        x[j] = keep ? x[j] : 0.f;
+                        for (uint32_t j = 0; j < kAc; ++j) x[j] = 0.f;
+                    } else if (!all_keep) {
+#pragma unroll
+                        for (uint32_t j = 0; j < kAc; ++j) {
+                            const bool keep = P.rev ? (j0 + j >= rho) : (j0 + j <= rho);
+                            x[j] = keep ? x[j] : 0.f;
+                        }
                     }
                     store_row_f16<kAc / 8>(a16, rho, j0 >> 3, x);
                 } else {
