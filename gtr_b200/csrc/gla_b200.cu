@@ -89,6 +89,27 @@ constexpr int kMinAutoCps = 4;   // smallest automatic segment length; also size
 
 int num_chunks(int T) { return (T + gla::kChunk - 1) / gla::kChunk; }
 
+// Segment length that minimises a simple cost model of the persistent kernel: the work items
+// (sequences x segments) run in rounds of `slots` CTAs; an item costs its chunks once for the
+// output pass plus about half of that for the state-only pre-pass every segment but the last
+// needs.  One segment per sequence avoids the pre-pass but leaves slots idle when there are few
+// sequences; many segments fill the machine but pay the pre-pass and round up to whole rounds.
+int auto_chunks_per_segment(int NT, int nseq, int slots) {
+    int best_cps = NT;
+    double best = 1e300;
+    for (int cps = NT; cps >= 1; --cps) {
+        const int ns = (NT + cps - 1) / cps;
+        if (ns > 1 && cps < kMinAutoCps) break;
+        if (cps != (NT + ns - 1) / ns) continue;               // only the balanced split for each segment count
+        const long items = static_cast<long>(nseq) * ns;
+        const long rounds = (items + slots - 1) / slots;
+        const double per_item = cps * (1.0 + (ns > 1 ? 0.5 * (ns - 1) / ns : 0.0)) + (ns > 1 ? 1.0 : 0.0);
+        const double cost = rounds * per_item;
+        if (cost < best - 1e-9) { best = cost; best_cps = cps; }
+    }
+    return best_cps;
+}
+
 // ---- tensor maps ------------------------------------------------------------------------
 struct MapKey {
     const void* ptr[gla::kNumTensors];
@@ -305,14 +326,7 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     }
     int cps;
     if (a->segments > 0) cps = a->segments;
-    else if (nseq >= slots) cps = NT;
-    else {
-        // aim for slightly more work items than CTA slots: few, long segments keep the share of the
-        // state-only pre-pass and of the look-back small
-        const int per_seq = (slots + nseq - 1) / nseq;          // segments per sequence for one full wave
-        cps = (NT + per_seq - 1) / per_seq;
-        if (cps < kMinAutoCps) cps = kMinAutoCps;
-    }
+    else cps = auto_chunks_per_segment(NT, nseq, slots);
     if (cps > NT) cps = NT;
     const int NS = (NT + cps - 1) / cps;
     const WsLayout L = ws_layout(static_cast<size_t>(nseq), static_cast<size_t>(NS));

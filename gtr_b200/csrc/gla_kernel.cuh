@@ -57,9 +57,9 @@ constexpr int kComputeThreads = 32 * kComputeWarps;
 constexpr int kThreads = 2 * kComputeThreads + 96;   // + TMA producer, score-MMA issuer, output/state-MMA issuer
 constexpr int kRowsPerThread = kChunk / kComputeWarps;   // gate math: logical rows per thread
 constexpr int kColSplit = kComputeWarps / 4;
-constexpr int kTmemCols = 128;
+constexpr int kTmemCols = 256;
 constexpr uint32_t kTmA = 0;              // scores: two buffers of 32 columns, each two interleaved halves
-constexpr uint32_t kTmOS = 64;            // outputs (lane offset 0) and state increment (lane offset 16)
+constexpr uint32_t kTmOS = 64;            // two buffers of 64 columns: outputs (lane offset 0), state increment (lane offset 16)
 constexpr int kSlots = kNumStages;        // per-chunk exchange slots (chunk totals, exact-path flag), one per stage
 constexpr uint32_t kLane16 = 16u << 16;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -124,7 +124,7 @@ struct Misc {
     uint64_t empty[kNumStages];
     // A barrier may run at most one phase ahead of its slowest waiter.  Barriers whose producer can run further
     // ahead are rings indexed like the resource they guard (stage, or tf32 buffer / score accumulator).
-    uint64_t ops_ready[kNumStages], a_done[2], a_free[2], a16_ready[2], os_done, acc_free, s16_ready;
+    uint64_t ops_ready[kNumStages], a_done[2], a_free[2], a16_ready[2], os_done[2], os_free[2], s16_ready;
     uint32_t tmem_base;
     volatile uint32_t abort;
     int item;
@@ -162,15 +162,17 @@ __device__ __forceinline__ void raise_timeout(const Ctx& c, uint32_t where) {
 // Bounded wait.  After a time-out in this CTA every later wait returns at once, so all warps
 // keep following the protocol (arrivals, named barriers) and the CTA drains and exits; the
 // result is then undefined and the status word says so.
-#ifndef GLA_SPIN_SLEEP_NS
-#define GLA_SPIN_SLEEP_NS 100
+#ifndef GLA_SPIN_SLEEP_MAX_NS
+#define GLA_SPIN_SLEEP_MAX_NS 512
 #endif
 __device__ __noinline__ void mbar_wait_slow(const Ctx& c, uint32_t b, uint32_t parity) {
     const uint64_t t0 = globaltimer_ns();
-    uint32_t n = 0;
+    uint32_t n = 0, ns = 32;
     while (true) {
         if (mbar_try_wait(b, parity)) return;
-        __nanosleep(GLA_SPIN_SLEEP_NS);   // a sleeping warp issues nothing; a polling one competes with working warps
+        // a sleeping warp issues nothing, a polling one competes with the working warps: back off quickly
+        __nanosleep(ns);
+        if (ns < GLA_SPIN_SLEEP_MAX_NS) ns <<= 1;
         if ((++n & 63u) == 0u) {
             if (c.misc->abort) return;
             if (globaltimer_ns() - t0 > c.deadline_span_ns) {
@@ -588,9 +590,9 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             mbar_init(smem_u32(&M.a_done[b]), 1);
             mbar_init(smem_u32(&M.a_free[b]), kComputeThreads);
             mbar_init(smem_u32(&M.a16_ready[b]), kComputeThreads);
+            mbar_init(smem_u32(&M.os_done[b]), 1);
+            mbar_init(smem_u32(&M.os_free[b]), kComputeThreads);
         }
-        mbar_init(smem_u32(&M.os_done), 1);
-        mbar_init(smem_u32(&M.acc_free), kComputeThreads);
         mbar_init(smem_u32(&M.s16_ready), kComputeThreads);
         M.abort = 0;
         fence_mbar_init();
@@ -611,7 +613,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     //   ctr  chunks seen so far (both passes): stage = ctr % kNumStages, exchange slot = ctr % kSlots
     //   c2   output-pass chunks seen so far: tf32 buffer / score accumulator = c2 & 1
     uint32_t ctr = 0, c2 = 0;
-    uint32_t n_s16 = 0, n_accfree = 0, n_osdone = 0;   // single barriers: use counts (MMA / epilogue roles)
+    uint32_t n_s16 = 0;   // single barrier: use count (output-MMA role)
 
     while (true) {
         if (tid == 0) M.item = static_cast<int>(atomicAdd(P.ctrl, 1u));
@@ -696,26 +698,34 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         const uint64_t dq = umma_desc_sw128(stage), dk = umma_desc_sw128(stage + kTileBytes, 8192),
                                        da16 = umma_desc_sw128(stage + 2 * kTileBytes),
                                        dv = umma_desc_sw128(stage + 3 * kTileBytes, 8192);
+                        // The O / state-increment accumulators are double-buffered: everything of this chunk that
+                        // does not need the incoming state (A.v and kh^T.v) is issued while the epilogue still works
+                        // on the previous chunk; only the read-out qh.S waits for the state, so the serial chain
+                        // from one chunk's state to the next is one short MMA group.
+                        const uint32_t p = ctr & 1u;
+                        const uint32_t tmOp = tmO + 64u * p, tmSp = tmS + 64u * p;
                         mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);          // v arrives by TMA
                         mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);     // qh, kh written in place
-                        if (!state_only) mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
-                        // both accumulators of the O/S columns must have been read by the epilogue
-                        mbar_wait(ctx, &M.acc_free, (n_accfree++ & 1u) ^ 1u);
+                        mbar_wait(ctx, &M.os_free[p], ((ctr >> 1) & 1u) ^ 1u);        // epilogue has read this buffer's previous use
                         GLA_EV(22);
                         tc_fence_after();
                         if (!state_only) {
-#pragma unroll
-                            for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmO, dq + ks * 2u, dS16 + ks * 128u, idO, ks);
                             mbar_wait(ctx, &M.a16_ready[c2 & 1u], (c2 >> 1) & 1u);
                             GLA_EV(23);
                             tc_fence_after();
 #pragma unroll
-                            for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmO, da16 + ks * 2u, dv + ks * 128u, idO, 1);
-                            ++c2;
+                            for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmOp, da16 + ks * 2u, dv + ks * 128u, idO, ks);
                         }
 #pragma unroll
-                        for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmS, dk + ks * 128u, dv + ks * 128u, idS, ks);
-                        umma_commit(smem_u32(&M.os_done));
+                        for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmSp, dk + ks * 128u, dv + ks * 128u, idS, ks);
+                        if (!state_only) {
+                            mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
+                            tc_fence_after();
+#pragma unroll
+                            for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmOp, dq + ks * 2u, dS16 + ks * 128u, idO, 1);
+                            ++c2;
+                        }
+                        umma_commit(smem_u32(&M.os_done[p]));
                         GLA_EV(24);
                     }
                 }
@@ -908,13 +918,14 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     }
                     // lanes 0-15: outputs -> scale -> fp16 tile (takes the place of qh) -> TMA store
                     // lanes 16-31: S <- 2^(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
-                    mbar_wait(ctx, &M.os_done, n_osdone++ & 1u);
+                    const uint32_t p = ctr & 1u;
+                    mbar_wait(ctx, &M.os_done[p], (ctr >> 1) & 1u);
                     GLA_EV(14);
                     tc_fence_after();
                     float x[kSc];
-                    tmem_row<kSc>(tmem, quad, kTmOS + col0, x);
+                    tmem_row<kSc>(tmem, quad, kTmOS + 64u * p + col0, x);
                     tc_fence_before();
-                    mbar_arrive(smem_u32(&M.acc_free));
+                    mbar_arrive(smem_u32(&M.os_free[p]));
                     const float b4 = ld_shared_f(smem_u32(&M.b4s[ctr % kSlots][my_c]));
                     const float dec = owner ? ex2(b4) : 0.f;
                     const float mul = owner ? 1.f : P.scale;
