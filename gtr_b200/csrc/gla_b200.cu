@@ -346,7 +346,8 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     P.NS = NS; P.cps = cps;
     P.num_items = nseq * NS;
     P.gated = gated ? 1 : 0;
-    P.scale = a->scale;
+    if (a->scale > 0.f && a->scale < 3.0e38f) { P.q_exp = log2f(a->scale); P.q_mul = a->scale; P.o_mul = 1.f; }
+    else { P.q_exp = 0.f; P.q_mul = 1.f; P.o_mul = a->scale; }
     P.inv_norm = a->gk_normalizer > 0.f ? 1.f / a->gk_normalizer : 0.f;
     P.rms_eps = a->rms_eps;
     P.rms_w = gated ? static_cast<const __half*>(a->rms_weight) : nullptr;
@@ -357,6 +358,8 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
         if (rc != GLA_B200_OK) return rc;
         P.gate_sb = gs[0]; P.gate_st = gs[1]; P.gate_sh = gs[2];
     }
+    P.o = static_cast<__half*>(a->o);
+    P.o_sb = key.stride[gla::TO][0]; P.o_st = key.stride[gla::TO][1]; P.o_sh = key.stride[gla::TO][2];
     P.s0 = a->initial_state;
     P.sT = a->final_state;
     P.ctrl = reinterpret_cast<uint32_t*>(ws + L.ctrl);

@@ -54,13 +54,13 @@ constexpr int kNumStages = GLA_STAGES;
 // split its columns.
 constexpr int kComputeWarps = GLA_COMPUTE_WARPS;
 constexpr int kComputeThreads = 32 * kComputeWarps;
-constexpr int kThreads = 2 * kComputeThreads + 96;   // + TMA producer, score-MMA issuer, output/state-MMA issuer
+constexpr int kThreads = 2 * kComputeThreads + 128;  // + TMA producer, score-MMA issuer, output/state-MMA issuer, store warp
 constexpr int kRowsPerThread = kChunk / kComputeWarps;   // gate math: logical rows per thread
 constexpr int kColSplit = kComputeWarps / 4;
 constexpr int kTmemCols = 256;
 constexpr uint32_t kTmA = 0;              // scores: two buffers of 32 columns, each two interleaved halves
 constexpr uint32_t kTmOS = 64;            // two buffers of 64 columns: outputs (lane offset 0), state increment (lane offset 16)
-constexpr int kSlots = kNumStages;        // per-chunk exchange slots (chunk totals, exact-path flag), one per stage
+constexpr int kSlots = 2 * kNumStages;    // per-chunk exchange slots (chunk totals, exact-path flag): outlive the stage
 constexpr uint32_t kLane16 = 16u << 16;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kWideLimit = 64.f * kLog2e;   // largest in-chunk decay (log2 units) the tf32 path takes
@@ -80,12 +80,16 @@ struct Params {
     int NS, cps;         // segments per sequence, chunks per segment
     int num_items;
     int gated;           // fused RMSNorm * w * silu(gate) epilogue
-    float scale;
+    // The output scale is folded into the exponent of the q-side gate factors (q_exp = log2(scale), o_mul = 1)
+    // when it is positive and finite; otherwise the epilogue multiplies (q_exp = 0, o_mul = scale).
+    float q_exp, q_mul, o_mul;
     float inv_norm;      // 1/gk_normalizer, or 0 when g already is a log gate
     float rms_eps;
     const __half* rms_w;      // [64]
     const __half* gate;       // output gate [B,T,H,64] with element strides gate_sb/st/sh
     long long gate_sb, gate_st, gate_sh;
+    __half* o;                // output [B,T,H,64] with element strides o_sb/st/sh
+    long long o_sb, o_st, o_sh;
     const float* s0;
     float* sT;
     uint32_t* ctrl;      // [0] ticket, [1] status
@@ -115,7 +119,8 @@ constexpr int kOffQbar = kNumStages * kStageBytes;       // two buffers of {qb 1
 constexpr int kQkBufBytes = 4 * kTileBytes;
 constexpr int kOffKbarRel = 2 * kTileBytes;              // kb inside a buffer
 constexpr int kOffS16 = kOffQbar + 2 * kQkBufBytes;
-constexpr int kOffMisc = kOffS16 + kTileBytes;
+constexpr int kOffOut = kOffS16 + kTileBytes;            // two output tiles (fp16, swizzled), sent out by the store warp
+constexpr int kOffMisc = kOffOut + 2 * kTileBytes;
 constexpr int kMiscBytes = 4096 + 512 * kComputeWarps;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + alignment slack
 
@@ -124,6 +129,7 @@ struct Misc {
     uint64_t empty[kNumStages];
     // A barrier may run at most one phase ahead of its slowest waiter.  Barriers whose producer can run further
     // ahead are rings indexed like the resource they guard (stage, or tf32 buffer / score accumulator).
+    uint64_t o_ready[2], o_free[2];
     uint64_t ops_ready[kNumStages], a_done[2], a_free[2], a16_ready[2], os_done[2], os_free[2], s16_ready;
     uint32_t tmem_base;
     volatile uint32_t abort;
@@ -131,7 +137,7 @@ struct Misc {
     uint32_t wide[kSlots];
     alignas(16) float tot[2][kComputeWarps][kD];   // per-warp gate sums (float2 access), double-buffered
     alignas(16) float b4s[kSlots][kD]; // chunk totals G_L per channel
-    float ssq[kColSplit][kChunk];      // fused epilogue: per-row partial sums of squares
+    float ssq[2][kColSplit][kChunk];   // fused epilogue: per-row partial sums of squares, by chunk parity
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "misc block too large");
 
@@ -162,18 +168,20 @@ __device__ __forceinline__ void raise_timeout(const Ctx& c, uint32_t where) {
 // Bounded wait.  After a time-out in this CTA every later wait returns at once, so all warps
 // keep following the protocol (arrivals, named barriers) and the CTA drains and exits; the
 // result is then undefined and the status word says so.
-#ifndef GLA_SPIN_SLEEP_MAX_NS
-#define GLA_SPIN_SLEEP_MAX_NS 512
+// Every polling thread is on the path of a stage through the pipeline (the stage ring is only kNumStages deep, so
+// the time a stage spends between its TMA load and its release bounds the throughput): no sleeping between polls --
+// try_wait itself suspends the thread for a while -- and only one warp per group and one lane per single-thread
+// role ever polls.
+#ifndef GLA_SPIN_SLEEP_NS
+#define GLA_SPIN_SLEEP_NS 0
 #endif
 __device__ __noinline__ void mbar_wait_slow(const Ctx& c, uint32_t b, uint32_t parity) {
     const uint64_t t0 = globaltimer_ns();
-    uint32_t n = 0, ns = 32;
+    uint32_t n = 0;
     while (true) {
         if (mbar_try_wait(b, parity)) return;
-        // a sleeping warp issues nothing, a polling one competes with the working warps: back off quickly
-        __nanosleep(ns);
-        if (ns < GLA_SPIN_SLEEP_MAX_NS) ns <<= 1;
-        if ((++n & 63u) == 0u) {
+        if (GLA_SPIN_SLEEP_NS > 0) __nanosleep(GLA_SPIN_SLEEP_NS);
+        if ((++n & 255u) == 0u) {
             if (c.misc->abort) return;
             if (globaltimer_ns() - t0 > c.deadline_span_ns) {
                 raise_timeout(c, WHERE_MBAR);
@@ -188,26 +196,67 @@ __device__ __forceinline__ void mbar_wait(const Ctx& c, uint64_t* bar, uint32_t 
     mbar_wait_slow(c, b, parity);
 }
 
-// Enumerate the TMA boxes that cover chunk [p0, p0+64) of the scan.  f(box_id, r, c, smem_row).
-template <class F>
-__device__ __forceinline__ void for_each_box(int p0, int L, int Hc, int rev, F f) {
-    const int u_lo = rev ? (L - p0 - kChunk) : p0;
-    int u0 = max(u_lo, 0);
-    const int u1 = min(u_lo + kChunk, L);
-    while (u0 < u1) {
-        const int c = u0 / Hc;
-        int r = u0 - c * Hc;
-        int len = min(Hc - r, u1 - u0);
-        while (len > 0) {
-            const int id = len >= 64 ? 0 : len >= 16 ? 1 : len >= 4 ? 2 : 3;
-            const int R = 64 >> (2 * id);
-            f(id, r, c, u0 - u_lo);
-            r += R;
-            u0 += R;
-            len -= R;
+// Wait of a whole warp group: its first warp polls the mbarrier, the others sleep in the hardware barrier
+// `bar_id` (a warp parked in bar.sync issues nothing, a polling warp competes with the working ones).
+__device__ __forceinline__ void group_wait(const Ctx& c, uint64_t* bar, uint32_t parity, int group_warp, uint32_t bar_id) {
+    if (group_warp == 0) mbar_wait(c, bar, parity);
+    named_bar_sync(bar_id, kComputeThreads);
+}
+
+// One arrival per warp: the lanes order their work before lane 0 with a warp barrier, lane 0 arrives for all of
+// them.  (Per-thread arrivals are 32 serialized updates of one shared-memory word per warp.)
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(bar));
+}
+
+// Walks the chunks of one pass along the scan and enumerates, for the current chunk, the TMA boxes that cover
+// it: f(box_id, r, c, smem_row) with (r, c) the row inside the column and the column where the box starts.  The
+// position is advanced chunk by chunk, so the loop needs no division.
+struct BoxWalker {
+    int u_lo;     // scan position of the chunk's first row (may be negative for the ragged chunk of a reversed scan)
+    int c, r;     // column and row inside the column of max(u_lo, 0)
+    __device__ __forceinline__ BoxWalker(const Params& P, int p0) {
+        u_lo = P.rev ? (P.T - p0 - kChunk) : p0;
+        const int u0 = max(u_lo, 0);
+        c = u0 / P.Hc;
+        r = u0 - c * P.Hc;
+    }
+    template <class F>
+    __device__ __forceinline__ void for_each(const Params& P, F f) const {
+        int u0 = max(u_lo, 0);
+        const int u1 = min(u_lo + kChunk, P.T);
+        int cc = c, rr = r;
+        while (u0 < u1) {
+            int len = min(P.Hc - rr, u1 - u0);
+            while (len > 0) {
+                const int id = len >= 64 ? 0 : len >= 16 ? 1 : len >= 4 ? 2 : 3;
+                const int R = 64 >> (2 * id);
+                f(id, rr, cc, u0 - u_lo);
+                rr += R;
+                u0 += R;
+                len -= R;
+            }
+            if (rr >= P.Hc) { rr = 0; ++cc; }
         }
     }
-}
+    __device__ __forceinline__ void advance(const Params& P) {
+        if (!P.rev) {
+            u_lo += kChunk;
+            r += kChunk;
+            while (r >= P.Hc) { r -= P.Hc; ++c; }
+        } else {
+            u_lo -= kChunk;
+            if (u_lo >= 0) {
+                r -= kChunk;
+                while (r < 0) { r += P.Hc; --c; }
+            } else {
+                c = 0;
+                r = 0;
+            }
+        }
+    }
+};
 
 __device__ __forceinline__ int chunk_valid(int p0, int L) { return min(kChunk, L - p0); }
 
@@ -231,8 +280,10 @@ __device__ __noinline__ void logits_to_log_gates(uint8_t* tg, float inv_norm, in
 
 #ifdef GLA_TRACE
 #define GLA_DBG(bit) ((c.p->dbg >> (bit)) & 1)
+#define GLA_DBGP(bit) ((P.dbg >> (bit)) & 1)
 #else
 #define GLA_DBG(bit) 0
+#define GLA_DBGP(bit) 0
 #endif
 // Gate math for one chunk (all compute threads).  Thread (w, l) owns logical rows
 // 8w..8w+7 and channels 2l, 2l+1.  Logical row = position inside the chunk along the scan;
@@ -279,6 +330,7 @@ template <bool kRev>
 __device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, uint32_t qbar, int valid, int w, int l,
                                                bool state_only, bool wide, float off0, float off1, float b40, float b41, float e10,
                                                float e11, float e20, float e21) {
+    const float qx = c.p->q_exp;
     const GateLane gl = gate_lane<kRev>(w, l);
     const uint32_t tq = stage, tk = stage + kTileBytes, tg = stage + 2 * kTileBytes, tv = stage + 3 * kTileBytes;
     const uint32_t kbar = qbar + kOffKbarRel;
@@ -299,7 +351,7 @@ __device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, uin
         sts32(tk + o16, pack_half2_sat(kh0, kh1));
         if (!live) sts32(tv + o16, 0u);                // rows past the end must be finite for the MMAs
         if (!state_only) {
-            const float qh0 = qv.x * ex2(a0), qh1 = qv.y * ex2(a1);
+            const float qh0 = qv.x * ex2(a0 + qx), qh1 = qv.y * ex2(a1 + qx);
             sts32(tq + o16, pack_half2_sat(qh0, qh1));
             if (!wide) {
                 sts64(qbar + o32, round_tf32(qh0 * e10), round_tf32(qh1 * e11));
@@ -315,7 +367,8 @@ __device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, uin
 }
 
 template <bool kStateOnly, bool kRev>
-__device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, uint32_t qbar, int n, int valid, int w, int l) {
+__device__ __forceinline__ bool gate_math_t(const Ctx& c, uint32_t stage, uint32_t qbar, int n, int valid, int w, int l,
+                                            uint64_t* buf_bar, uint32_t buf_parity) {
     constexpr int R = kRowsPerThread;
     static_assert(R == 8 || R == 4, "the swizzle shortcut needs a row count that divides 8");
     const Params& P = *c.p;
@@ -370,6 +423,9 @@ __device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, uint32
         sts64(tot_sa + w * kD * 4, a0, a1);
     }
     GLA_EVC(c, 40);
+    // the tf32 buffer written below is free once the score MMAs of its previous use have completed; one warp
+    // polls for that, the exchange barrier tells the others
+    if (!kStateOnly && w == 0) mbar_wait(c, buf_bar, buf_parity);
     named_bar_sync(1, kComputeThreads);
     GLA_EVC(c, 41);
     float off0 = 0.f, off1 = 0.f, b40 = 0.f, b41 = 0.f, gm0 = 0.f, gm1 = 0.f;
@@ -397,14 +453,15 @@ __device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, uint32
     } else {
         // straight-line: exponents first, then products, then stores
         const float ck0 = b40 - off0, ck1 = b41 - off1;
+        const float oq0 = off0 + P.q_exp, oq1 = off1 + P.q_exp;
         float ek0[R], ek1[R], eq0[R], eq1[R];
 #pragma unroll
         for (int i = 0; i < R; ++i) {
             ek0[i] = ex2(ck0 - cs0[i]);
             ek1[i] = ex2(ck1 - cs1[i]);
             if (!kStateOnly) {
-                eq0[i] = ex2(off0 + cs0[i]);
-                eq1[i] = ex2(off1 + cs1[i]);
+                eq0[i] = ex2(oq0 + cs0[i]);
+                eq1[i] = ex2(oq1 + cs1[i]);
             }
         }
 #pragma unroll
@@ -426,17 +483,18 @@ __device__ __forceinline__ void gate_math_t(const Ctx& c, uint32_t stage, uint32
     GLA_EVC(c, 42);
     fence_proxy_async_smem();
     GLA_EVC(c, 43);
+    return wide;
 }
 
-__device__ __forceinline__ void gate_math(const Ctx& c, uint32_t stage, uint32_t qbar, int n, int valid, int w, int l,
-                                          bool state_only) {
+// Returns whether the chunk took the exact-score path (always false for state-only chunks).
+__device__ __forceinline__ bool gate_math(const Ctx& c, uint32_t stage, uint32_t qbar, int n, int valid, int w, int l,
+                                          bool state_only, uint64_t* buf_bar, uint32_t buf_parity) {
     if (c.p->rev) {
-        if (state_only) gate_math_t<true, true>(c, stage, qbar, n, valid, w, l);
-        else gate_math_t<false, true>(c, stage, qbar, n, valid, w, l);
-    } else {
-        if (state_only) gate_math_t<true, false>(c, stage, qbar, n, valid, w, l);
-        else gate_math_t<false, false>(c, stage, qbar, n, valid, w, l);
+        if (state_only) return gate_math_t<true, true>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity);
+        return gate_math_t<false, true>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity);
     }
+    if (state_only) return gate_math_t<true, false>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity);
+    return gate_math_t<false, false>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity);
 }
 
 __device__ __forceinline__ uint32_t sw_f16(uint32_t row, uint32_t col) {     // col in fp16 elements
@@ -465,6 +523,7 @@ __device__ __noinline__ void exact_scores(const Ctx& c, uint8_t* a16_tile, const
                 s += qv.y * kv.y * ex2(gi.y - gj.y);
             }
         }
+        s *= c.p->q_mul;
         const __half hv = __float2half_rn(fminf(fmaxf(s, -65504.f), 65504.f));
         *reinterpret_cast<__half*>(a16_tile + sw_f16(i, j)) = hv;
     }
@@ -547,10 +606,14 @@ __device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
 }
 
 // Warp roles (one CTA per SM):
-//   warps 0..7   gate group     raw q,k,g tiles -> qh, kh (fp16, in place) and qb, kb (tf32, two buffers)
-//   warps 8..15  epilogue group TMEM read-out: scores -> fp16 tile, outputs -> tile -> TMA store, state in fp32
+//   warps 0..7   epilogue group TMEM read-out: scores -> fp16 tile, outputs -> tile -> TMA store, state in fp32
 //                               registers, look-back and publication of segment states
-//   warp 16      TMA producer   warp 17  score MMAs   warp 18  output and state MMAs
+//   warps 8..15  gate group     raw q,k,g tiles -> qh, kh (fp16, in place) and qb, kb (tf32, two buffers)
+//   warp 16      TMA producer   warp 17  score MMAs   warp 18  output and state MMAs   warp 19  output TMA stores
+// The epilogue group is the serial chain of a sequence (state in, state out) and its code is one long
+// dependency chain; the gate group is throughput work with slack and plenty of independent instructions.
+// The warp scheduler favours the lower warp ids when several warps are ready, so the epilogue group takes them:
+// with the gate group first, epilogue instructions waited ~15 cycles each whenever the gate math was running.
 // (one thread needs ~100 cycles to issue a tcgen05.mma whatever its shape, so the 28 small MMAs of a chunk
 // are issued from two threads)
 // The gate group runs up to two chunks ahead of the epilogue group (bounded by the tf32 buffers), so operand
@@ -585,16 +648,21 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             mbar_init(smem_u32(&M.full[s]), 1);
             mbar_init(smem_u32(&M.empty[s]), 1);
         }
-        for (int s = 0; s < kNumStages; ++s) mbar_init(smem_u32(&M.ops_ready[s]), kComputeThreads);
+        for (int s = 0; s < kNumStages; ++s) mbar_init(smem_u32(&M.ops_ready[s]), kComputeWarps);
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&M.a_done[b]), 1);
-            mbar_init(smem_u32(&M.a_free[b]), kComputeThreads);
-            mbar_init(smem_u32(&M.a16_ready[b]), kComputeThreads);
+            mbar_init(smem_u32(&M.a_free[b]), kComputeWarps);
+            mbar_init(smem_u32(&M.a16_ready[b]), kComputeWarps);
             mbar_init(smem_u32(&M.os_done[b]), 1);
-            mbar_init(smem_u32(&M.os_free[b]), kComputeThreads);
+            mbar_init(smem_u32(&M.os_free[b]), kComputeWarps);
+            mbar_init(smem_u32(&M.o_ready[b]), kComputeWarps);
+            mbar_init(smem_u32(&M.o_free[b]), 1);
         }
-        mbar_init(smem_u32(&M.s16_ready), kComputeThreads);
+        mbar_init(smem_u32(&M.s16_ready), kComputeWarps);
         M.abort = 0;
+#ifdef GLA_TRACE
+        for (int i = 0; i < kSlots; ++i) M.wide[i] = 0;
+#endif
         fence_mbar_init();
     }
     if (w == kWarpProducer) {
@@ -607,38 +675,44 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = M.tmem_base;
+    const uint32_t tmem = __shfl_sync(0xffffffffu, M.tmem_base, 0);
 
     // Every role walks the same sequence of chunks and keeps its own counters:
     //   ctr  chunks seen so far (both passes): stage = ctr % kNumStages, exchange slot = ctr % kSlots
     //   c2   output-pass chunks seen so far: tf32 buffer / score accumulator = c2 & 1
     uint32_t ctr = 0, c2 = 0;
     uint32_t n_s16 = 0;   // single barrier: use count (output-MMA role)
+    uint32_t wide_hist = 0;   // gate group: bit b = the last chunk in tf32 buffer b took the exact path
 
     while (true) {
         if (tid == 0) M.item = static_cast<int>(atomicAdd(P.ctrl, 1u));
         __syncthreads();
-        const int item = M.item;
+        const int item = __shfl_sync(0xffffffffu, M.item, 0);   // known to be warp-uniform
         if (item >= P.num_items) break;
         const ItemInfo it = decode_item(P, item);
         const int npass = it.state_pass ? 2 : 1;
 
+        // The four service warps below run their loops with all 32 lanes, in warp-uniform control flow, and only the
+        // issue of an asynchronous instruction (TMA, tcgen05.mma, commit) is left to one elected lane.  Loop
+        // counters, descriptors and coordinates then live in uniform registers, which is what those instructions
+        // take; a loop run by a single lane inside a divergent branch pays a move from the vector registers per
+        // operand and needs three times as long per MMA.
         if (w == kWarpProducer) {
             // ------------------------------------------------------------ TMA producer
-            if (l == 0) {
-                for (int pass = 0; pass < npass; ++pass) {
-                    const bool state_only = it.state_pass && pass == 0;
-                    for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                        const uint32_t s = ctr % kNumStages, n = ctr / kNumStages;
-                        mbar_wait(ctx, &M.empty[s], (n & 1u) ^ 1u);
-                        GLA_EV(30);
-                        const int p0 = (it.first_chunk + i) * kChunk;
-                        const int valid = chunk_valid(p0, P.T);
+            for (int pass = 0; pass < npass; ++pass) {
+                const bool state_only = it.state_pass && pass == 0;
+                BoxWalker bw(P, it.first_chunk * kChunk);
+                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                    const uint32_t s = ctr % kNumStages, n = ctr / kNumStages;
+                    mbar_wait(ctx, &M.empty[s], (n & 1u) ^ 1u);
+                    GLA_EV(30);
+                    if (elect_one()) {
+                        const int valid = chunk_valid((it.first_chunk + i) * kChunk, P.T);
                         const int ntens = state_only ? 3 : 4;
                         const uint32_t bar = smem_u32(&M.full[s]);
                         mbar_arrive_expect_tx(bar, static_cast<uint32_t>(valid * 128 * ntens));
                         const uint32_t stage = base + kOffStage + s * kStageBytes;
-                        for_each_box(p0, P.T, P.Hc, P.rev, [&](int id, int r, int c, int row) {
+                        bw.for_each(P, [&](int id, int r, int c, int row) {
                             const uint32_t off = static_cast<uint32_t>(row) * 128u;
                             if (!state_only)
                                 tma_load_5d(stage + 0 * kTileBytes + off, &maps.m[TQ][id], bar, 0, it.h, r, c, it.b);
@@ -647,25 +721,27 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             tma_load_5d(stage + 3 * kTileBytes + off, &maps.m[TV][id], bar, 0, it.h, r, c, it.b);
                         });
                     }
+                    __syncwarp();
+                    bw.advance(P);
                 }
             }
-            __syncwarp();
         } else if (w == kWarpMma) {
             // ------------------------------------------------------------ score MMAs (output pass only)
-            if (l == 0) {
-                constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 32);
-                for (int pass = 0; pass < npass; ++pass) {
-                    const bool state_only = it.state_pass && pass == 0;
-                    for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                        const uint32_t s = ctr % kNumStages, b = c2 & 1u;
-                        // a parity wait only tells apart consecutive phases, so this thread has to observe
-                        // every phase of the ring, also those of state-only chunks it has nothing to do for
-                        mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);
-                        if (state_only) continue;
-                        mbar_wait(ctx, &M.a_free[b], ((c2 >> 1) & 1u) ^ 1u);   // epilogue done with this buffer's previous use
-                        GLA_EV(20);
-                        tc_fence_after();
-                        if (!M.wide[ctr % kSlots]) {
+            constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 32);
+            for (int pass = 0; pass < npass; ++pass) {
+                const bool state_only = it.state_pass && pass == 0;
+                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                    const uint32_t s = ctr % kNumStages, b = c2 & 1u;
+                    // a parity wait only tells apart consecutive phases, so this warp has to observe
+                    // every phase of the ring, also those of state-only chunks it has nothing to do for
+                    mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);
+                    if (state_only) continue;
+                    mbar_wait(ctx, &M.a_free[b], ((c2 >> 1) & 1u) ^ 1u);   // epilogue done with this buffer's previous use
+                    GLA_EV(20);
+                    tc_fence_after();
+                    const uint32_t wide = __shfl_sync(0xffffffffu, M.wide[ctr % kSlots], 0);
+                    if (elect_one()) {
+                        if (!wide && !GLA_DBGP(4)) {
                             const uint64_t dQ = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes);
                             const uint64_t dK = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes + kOffKbarRel);
                             const uint32_t tmA = tmem + kTmA + 32u * b;
@@ -677,78 +753,119 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             }
                         }
                         umma_commit(smem_u32(&M.a_done[b]));
-                        GLA_EV(21);
-                        ++c2;
                     }
+                    __syncwarp();
+                    GLA_EV(21);
+                    ++c2;
                 }
             }
-            __syncwarp();
         } else if (w == kWarpMma + 1) {
             // ------------------------------------------------------------ output and state MMAs
-            if (l == 0) {
-                constexpr uint32_t idO = umma_idesc(FMT_F16, 0, 1, 64, 64);
-                constexpr uint32_t idS = umma_idesc(FMT_F16, 1, 1, 64, 64);
-                const uint32_t tmO = tmem + kTmOS, tmS = tmem + kTmOS + kLane16;
-                const uint64_t dS16 = umma_desc_sw128(base + kOffS16, 8192);
-                for (int pass = 0; pass < npass; ++pass) {
-                    const bool state_only = it.state_pass && pass == 0;
-                    for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                        const uint32_t s = ctr % kNumStages;
-                        const uint32_t stage = base + kOffStage + s * kStageBytes;
-                        const uint64_t dq = umma_desc_sw128(stage), dk = umma_desc_sw128(stage + kTileBytes, 8192),
-                                       da16 = umma_desc_sw128(stage + 2 * kTileBytes),
-                                       dv = umma_desc_sw128(stage + 3 * kTileBytes, 8192);
-                        // The O / state-increment accumulators are double-buffered: everything of this chunk that
-                        // does not need the incoming state (A.v and kh^T.v) is issued while the epilogue still works
-                        // on the previous chunk; only the read-out qh.S waits for the state, so the serial chain
-                        // from one chunk's state to the next is one short MMA group.
-                        const uint32_t p = ctr & 1u;
-                        const uint32_t tmOp = tmO + 64u * p, tmSp = tmS + 64u * p;
-                        mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);          // v arrives by TMA
-                        mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);     // qh, kh written in place
-                        mbar_wait(ctx, &M.os_free[p], ((ctr >> 1) & 1u) ^ 1u);        // epilogue has read this buffer's previous use
-                        GLA_EV(22);
-                        tc_fence_after();
+            constexpr uint32_t idO = umma_idesc(FMT_F16, 0, 1, 64, 64);
+            constexpr uint32_t idS = umma_idesc(FMT_F16, 1, 1, 64, 64);
+            const uint32_t tmO = tmem + kTmOS, tmS = tmem + kTmOS + kLane16;
+            const uint64_t dS16 = umma_desc_sw128(base + kOffS16, 8192);
+            for (int pass = 0; pass < npass; ++pass) {
+                const bool state_only = it.state_pass && pass == 0;
+                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                    const uint32_t s = ctr % kNumStages;
+                    const uint32_t stage = base + kOffStage + s * kStageBytes;
+                    const uint64_t dq = umma_desc_sw128(stage), dk = umma_desc_sw128(stage + kTileBytes, 8192),
+                                   da16 = umma_desc_sw128(stage + 2 * kTileBytes),
+                                   dv = umma_desc_sw128(stage + 3 * kTileBytes, 8192);
+                    // The O / state-increment accumulators are double-buffered: everything of this chunk that
+                    // does not need the incoming state (A.v and kh^T.v) is issued while the epilogue still works
+                    // on the previous chunk; only the read-out qh.S waits for the state, so the serial chain
+                    // from one chunk's state to the next is one short MMA group.
+                    const uint32_t p = ctr & 1u;
+                    const uint32_t tmOp = tmO + 64u * p, tmSp = tmS + 64u * p;
+                    mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);          // v arrives by TMA
+                    mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);     // qh, kh written in place
+                    mbar_wait(ctx, &M.os_free[p], ((ctr >> 1) & 1u) ^ 1u);        // epilogue has read this buffer's previous use
+                    GLA_EV(22);
+                    if (!state_only) mbar_wait(ctx, &M.a16_ready[c2 & 1u], (c2 >> 1) & 1u);
+                    GLA_EV(23);
+                    tc_fence_after();
+                    if (elect_one() && !GLA_DBGP(5)) {
                         if (!state_only) {
-                            mbar_wait(ctx, &M.a16_ready[c2 & 1u], (c2 >> 1) & 1u);
-                            GLA_EV(23);
-                            tc_fence_after();
 #pragma unroll
                             for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmOp, da16 + ks * 2u, dv + ks * 128u, idO, ks);
                         }
 #pragma unroll
                         for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmSp, dk + ks * 128u, dv + ks * 128u, idS, ks);
-                        if (!state_only) {
-                            mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
-                            tc_fence_after();
+                    }
+                    __syncwarp();
+                    if (!state_only) {
+                        mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
+                        tc_fence_after();
+                        ++c2;
+                    }
+                    if (elect_one()) {
+                        if (!state_only && !GLA_DBGP(5)) {
 #pragma unroll
                             for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmOp, dq + ks * 2u, dS16 + ks * 128u, idO, 1);
-                            ++c2;
                         }
                         umma_commit(smem_u32(&M.os_done[p]));
-                        GLA_EV(24);
+                        // the same completion hands the stage back to the producer: gate math and the score MMAs are
+                        // long done with it, and nothing reads it after these MMAs
+                        umma_commit(smem_u32(&M.empty[s]));
                     }
+                    __syncwarp();
+                    GLA_EV(24);
                 }
             }
-            __syncwarp();
-        } else if (w < kComputeWarps) {
+        } else if (w == kWarpMma + 2) {
+            // ------------------------------------------------------------ store warp
+            // sends finished output tiles out by TMA (two tiles, so the epilogue of one chunk overlaps the store of
+            // the previous one)
+            for (int pass = 0; pass < npass; ++pass) {
+                if (it.state_pass && pass == 0) continue;
+                BoxWalker bw(P, it.first_chunk * kChunk);
+                for (int i = 0; i < it.nchunks; ++i, ++c2) {
+                    const uint32_t j = c2 & 1u;
+                    mbar_wait(ctx, &M.o_ready[j], (c2 >> 1) & 1u);
+                    if (elect_one()) {
+                        const uint32_t tile = base + kOffOut + j * kTileBytes;
+                        bw.for_each(P, [&](int id, int r, int c, int row) {
+                            tma_store_5d(&maps.m[TO][id], tile + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
+                        });
+                        tma_store_commit();
+                        tma_store_wait_read();
+                        mbar_arrive(smem_u32(&M.o_free[j]));
+                    }
+                    __syncwarp();
+                    bw.advance(P);
+                }
+            }
+        } else if (w >= kComputeWarps) {
             // ------------------------------------------------------------ gate group
+            const int gw = w - kComputeWarps;
             for (int pass = 0; pass < npass; ++pass) {
                 const bool state_only = it.state_pass && pass == 0;
                 for (int i = 0; i < it.nchunks; ++i, ++ctr) {
                     const uint32_t s = ctr % kNumStages;
                     mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);
                     uint32_t qbar = 0;
+                    uint64_t* buf_bar = nullptr;
+                    uint32_t buf_parity = 0;
                     if (!state_only) {
                         const uint32_t b = c2 & 1u;
-                        mbar_wait(ctx, &M.a_free[b], ((c2 >> 1) & 1u) ^ 1u);   // buffer's previous scores consumed
+                        // the buffer is free once the score MMAs of its previous use have completed (a_done); if that
+                        // use stashed operands for the exact path, once the epilogue has read them (a_free)
+                        buf_bar = ((wide_hist >> b) & 1u) ? &M.a_free[b] : &M.a_done[b];
+                        buf_parity = ((c2 >> 1) & 1u) ^ 1u;
                         qbar = base + kOffQbar + b * kQkBufBytes;
-                        ++c2;
                     }
                     GLA_EV(12);
-                    gate_math(ctx, base + kOffStage + s * kStageBytes, qbar, static_cast<int>(ctr),
-                              chunk_valid((it.first_chunk + i) * kChunk, P.T), w, l, state_only);
-                    mbar_arrive(smem_u32(&M.ops_ready[s]));
+                    const bool was_wide = GLA_DBGP(0) ? false :
+                        gate_math(ctx, base + kOffStage + s * kStageBytes, qbar, static_cast<int>(ctr),
+                                  chunk_valid((it.first_chunk + i) * kChunk, P.T), gw, l, state_only, buf_bar, buf_parity);
+                    if (!state_only) {
+                        const uint32_t b = c2 & 1u;
+                        wide_hist = (wide_hist & ~(1u << b)) | ((was_wide ? 1u : 0u) << b);
+                        ++c2;
+                    }
+                    warp_arrive(&M.ops_ready[s], l);
                     GLA_EV(13);
                 }
             }
@@ -759,7 +876,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             // output row 16*(e&3) + l.
             constexpr int kSc = kD / kColSplit;       // O / state columns per thread
             constexpr int kAc = 32 / kColSplit;       // score columns per thread (per 32-column half)
-            const int e = w - kComputeWarps, etid = tid - kComputeThreads;
+            const int e = w, etid = tid;
             const bool owner = l >= 16;
             const int quad = e & 3, ch = e >> 2;
             const int my_c = 16 * quad + (l & 15);
@@ -798,37 +915,38 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             auto scores = [&](uint32_t cc, uint32_t k2) {
                 const uint32_t s = cc % kNumStages, b = k2 & 1u;
                 const uint32_t a16 = base + kOffStage + s * kStageBytes + 2 * kTileBytes;
-                mbar_wait(ctx, &M.a_done[b], (k2 >> 1) & 1u);
+                group_wait(ctx, &M.a_done[b], (k2 >> 1) & 1u, e, 2);
                 GLA_EV(10);
                 tc_fence_after();
-                if (!M.wide[cc % kSlots]) {
+                if (GLA_DBGP(2)) {
+                    warp_arrive(&M.a_free[b], l);
+                } else if (!M.wide[cc % kSlots]) {
                     float x[kAc];
                     tmem_row<kAc>(tmem, quad, kTmA + 32u * b + kAc * ch, x);
+                    GLA_EV(50);
                     tc_fence_before();
-                    mbar_arrive(smem_u32(&M.a_free[b]));
+                    warp_arrive(&M.a_free[b], l);
+                    GLA_EV(54);
                     const uint32_t j0 = (l >> 4) * 32u + kAc * ch;   // lanes 16-31 hold key rows 32-63
-                    // the block of 16 query rows (this quadrant) x kAc key columns lies before, on or after
-                    // the diagonal as a whole; only the diagonal block needs a per-element mask
-                    const uint32_t r0 = 16u * quad;
-                    const bool all_keep = P.rev ? (j0 >= r0 + 15u) : (j0 + kAc - 1u <= r0);
-                    const bool none = P.rev ? (j0 + kAc - 1u < r0) : (j0 > r0 + 15u);
-                    if (none) {
+                    // causal mask along the scan: keep key j0 + j at or before query rho (after it, reversed);
+                    // branch-free selects -- the two half-warps sit on different sides of the diagonal
+                    const int lim = static_cast<int>(rho) - static_cast<int>(j0);
+                    if (!P.rev) {
 #pragma unroll
-                        for (uint32_t j = 0; j < kAc; ++j) x[j] = 0.f;
-                    } else if (!all_keep) {
+                        for (int j = 0; j < kAc; ++j) x[j] = (j <= lim) ? x[j] : 0.f;
+                    } else {
 #pragma unroll
-                        for (uint32_t j = 0; j < kAc; ++j) {
-                            const bool keep = P.rev ? (j0 + j >= rho) : (j0 + j <= rho);
-                            x[j] = keep ? x[j] : 0.f;
-                        }
+                        for (int j = 0; j < kAc; ++j) x[j] = (j >= lim) ? x[j] : 0.f;
                     }
+                    GLA_EV(55);
                     store_row_f16<kAc / 8>(a16, rho, j0 >> 3, x);
+                    GLA_EV(51);
                 } else {
                     exact_scores(ctx, base_ptr + (a16 - base), base_ptr + kOffQbar + b * kQkBufBytes, etid);
-                    mbar_arrive(smem_u32(&M.a_free[b]));
+                    warp_arrive(&M.a_free[b], l);
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&M.a16_ready[b]));
+                warp_arrive(&M.a16_ready[b], l);
                 GLA_EV(11);
             };
 
@@ -905,88 +1023,112 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     }
                     if (owner) store_row_f16<kSc / 8>(base + kOffS16, rho, col0 >> 3, S);
                     fence_proxy_async_smem();
-                    mbar_arrive(smem_u32(&M.s16_ready));
+                    warp_arrive(&M.s16_ready, l);
                     scores(ctr, c2);
                 }
 
+                // position along the scan of this thread's output row in the pass's first chunk: u, and for
+                // column scans its column cc and row rr inside the column (floor division: u < 0 only for rows
+                // before the start of a reversed ragged chunk, which are never written)
+                int u = 0, rr = 0, cc = 0;
+                if (!state_only && P.gated) {
+                    const int p0 = it.first_chunk * kChunk;
+                    u = (P.rev ? (P.T - p0 - kChunk) : p0) + static_cast<int>(rho);
+                    if (P.Wc > 1) {
+                        cc = u / P.Hc;
+                        rr = u - cc * P.Hc;
+                        if (rr < 0) { rr += P.Hc; --cc; }
+                    }
+                }
                 for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                    const uint32_t s = ctr % kNumStages;
-                    const uint32_t stage = base + kOffStage + s * kStageBytes;
                     if (!state_only) {
                         if (i + 1 < it.nchunks) scores(ctr + 1, c2 + 1);   // overlaps the output/state MMAs of chunk i
                         ++c2;
                     }
-                    // lanes 0-15: outputs -> scale -> fp16 tile (takes the place of qh) -> TMA store
+                    // lanes 0-15: outputs -> scale -> fp16 -> global memory
                     // lanes 16-31: S <- 2^(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
                     const uint32_t p = ctr & 1u;
-                    mbar_wait(ctx, &M.os_done[p], (ctr >> 1) & 1u);
+                    group_wait(ctx, &M.os_done[p], (ctr >> 1) & 1u, e, 2);
                     GLA_EV(14);
                     tc_fence_after();
-                    float x[kSc];
-                    tmem_row<kSc>(tmem, quad, kTmOS + 64u * p + col0, x);
-                    tc_fence_before();
-                    mbar_arrive(smem_u32(&M.os_free[p]));
+                    // the exchange slot's chunk total first: its latency hides behind the TMEM read
                     const float b4 = ld_shared_f(smem_u32(&M.b4s[ctr % kSlots][my_c]));
-                    const float dec = owner ? ex2(b4) : 0.f;
-                    const float mul = owner ? 1.f : P.scale;
-                    if (owner) gsum += b4;
+                    if (GLA_DBGP(3)) {
+                        warp_arrive(&M.os_free[p], l);
+                    } else {
+                        float x[kSc];
+                        tmem_row<kSc>(tmem, quad, kTmOS + 64u * p + col0, x);
+                        GLA_EV(52);
+                        tc_fence_before();
+                        warp_arrive(&M.os_free[p], l);
+                        const float dec = owner ? ex2(b4) : 0.f;
+                        if (owner) gsum += b4;
 #pragma unroll
-                    for (int v = 0; v < kSc; ++v) {
-                        S[v] = fmaf(dec, S[v], x[v]);
-                        x[v] = S[v] * mul;
+                        for (int v = 0; v < kSc; ++v) S[v] = fmaf(dec, S[v], x[v]);   // lanes 0-15: dec = 0, S is the output row
                     }
-                    if (!state_only && P.gated) {
-                        // y = o * rsqrt(mean(o^2) + eps) * w * silu(gate); a row's 64 columns are split over
-                        // kColSplit warps, which exchange their partial sums of squares through shared memory
-                        float ss = 0.f;
+                    if (!state_only && GLA_DBGP(3)) {
+                        const uint32_t j = (c2 - 1u) & 1u;
+                        mbar_wait(ctx, &M.o_free[j], (((c2 - 1u) >> 1) & 1u) ^ 1u);
+                        if (i + 1 < it.nchunks) warp_arrive(&M.s16_ready, l);
+                        warp_arrive(&M.o_ready[j], l);
+                    } else if (!state_only) {
+                        if (P.gated) {
+                            // y = o * rsqrt(mean(o^2) + eps) * w * silu(gate); a row's 64 columns are split over
+                            // kColSplit warps, which exchange their partial sums of squares through shared memory
+                            float ss = 0.f;
 #pragma unroll
-                        for (int v = 0; v < kSc; ++v) ss = fmaf(x[v], x[v], ss);
-                        if (!owner) M.ssq[ch][rho] = ss;
-                        named_bar_sync(2, kComputeThreads);
-                        if (!owner) {
-                            float tot = 0.f;
-#pragma unroll
-                            for (int cc2 = 0; cc2 < kColSplit; ++cc2) tot += M.ssq[cc2][rho];
-                            const float rinv = rsqrtf(tot * (1.f / kD) + P.rms_eps);
+                            for (int v = 0; v < kSc; ++v) ss = fmaf(S[v], S[v], ss);
+                            const int par = ctr & 1u;
+                            if (!owner) M.ssq[par][ch][rho] = ss * (P.o_mul * P.o_mul);
+                            named_bar_sync(2, kComputeThreads);
                             // token read at this row of the chunk (same mapping as the TMA boxes)
-                            const int p0 = (it.first_chunk + i) * kChunk;
-                            const int u = (P.rev ? (P.T - p0 - kChunk) : p0) + static_cast<int>(rho);
-                            if (u >= 0 && u < P.T) {
-                                const int cc3 = u / P.Hc, rr = u - cc3 * P.Hc;
-                                const long long tok = (P.Wc > 1) ? static_cast<long long>(rr) * P.Wc + cc3 : u;
+                            if (!owner && u >= 0 && u < P.T) {
+                                float tot = 0.f;
+#pragma unroll
+                                for (int cc2 = 0; cc2 < kColSplit; ++cc2) tot += M.ssq[par][cc2][rho];
+                                const float rinv = P.o_mul * rsqrtf(tot * (1.f / kD) + P.rms_eps);
+                                const long long tok = (P.Wc > 1) ? static_cast<long long>(rr) * P.Wc + cc : u;
                                 const uint4* gp = reinterpret_cast<const uint4*>(
                                     P.gate + it.b * P.gate_sb + tok * P.gate_st + it.h * P.gate_sh + col0);
                                 const uint4* wp = reinterpret_cast<const uint4*>(P.rms_w + col0);
 #pragma unroll
-                                for (int v8 = 0; v8 < kSc / 8; ++v8) {
-                                    const uint4 g4 = __ldg(gp + v8), w4 = __ldg(wp + v8);
+                                for (int m = 0; m < kSc / 8; ++m) {
+                                    const uint4 g4 = __ldg(gp + m), w4 = __ldg(wp + m);
                                     const uint32_t gu[4] = {g4.x, g4.y, g4.z, g4.w}, wu[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
                                     for (int q2 = 0; q2 < 4; ++q2) {
                                         const float2 gf = unpack_half2(gu[q2]), wf = unpack_half2(wu[q2]);
-                                        x[8 * v8 + 2 * q2] *= rinv * wf.x * (gf.x / (1.f + __expf(-gf.x)));
-                                        x[8 * v8 + 2 * q2 + 1] *= rinv * wf.y * (gf.y / (1.f + __expf(-gf.y)));
+                                        S[8 * m + 2 * q2] *= rinv * wf.x * (gf.x / (1.f + __expf(-gf.x)));
+                                        S[8 * m + 2 * q2 + 1] *= rinv * wf.y * (gf.y / (1.f + __expf(-gf.y)));
                                     }
                                 }
                             }
+                            // next chunk: 64 steps further along the scan
+                            if (!P.rev) {
+                                u += kChunk;
+                                rr += kChunk;
+                                while (rr >= P.Hc) { rr -= P.Hc; ++cc; }
+                            } else {
+                                u -= kChunk;
+                                rr -= kChunk;
+                                while (rr < 0) { rr += P.Hc; --cc; }
+                            }
+                        } else if (P.o_mul != 1.f) {      // scale not folded into q (zero, negative or not finite)
+                            const float mul = owner ? 1.f : P.o_mul;
+#pragma unroll
+                            for (int v = 0; v < kSc; ++v) S[v] *= mul;
                         }
-                    }
-                    if (!state_only) {
-                        store_row_f16<kSc / 8>(owner ? base + kOffS16 : stage, rho, col0 >> 3, x);
+                        // lanes 16-31: fp16 copy of the new state for the next chunk's read-out;
+                        // lanes 0-15: output row into an output tile (the store warp sends it out); c2 already counts
+                        // this chunk
+                        const uint32_t j = (c2 - 1u) & 1u;
+                        mbar_wait(ctx, &M.o_free[j], (((c2 - 1u) >> 1) & 1u) ^ 1u);   // tile's previous store has read it
+                        store_row_f16<kSc / 8>(owner ? base + kOffS16 : base + kOffOut + j * kTileBytes, rho, col0 >> 3, S);
                         fence_proxy_async_smem();
-                        if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.s16_ready));
+                        if (i + 1 < it.nchunks) warp_arrive(&M.s16_ready, l);
+                        warp_arrive(&M.o_ready[j], l);
                         GLA_EV(15);
-                        named_bar_sync(2, kComputeThreads);
-                        if (etid == 0) {
-                            const int p0 = (it.first_chunk + i) * kChunk;
-                            for_each_box(p0, P.T, P.Hc, P.rev, [&](int id, int r, int c, int row) {
-                                tma_store_5d(&maps.m[TO][id], stage + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
-                            });
-                            tma_store_commit();
-                            tma_store_wait_read();
-                        }
                     }
-                    if (etid == 0) mbar_arrive(smem_u32(&M.empty[s]));
                     GLA_EV(16);
                 }
 
@@ -1009,7 +1151,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         __syncthreads();   // the item is drained: every role restarts from the same counters
     }
 
-    if (tid == kComputeThreads) tma_store_wait_all();
+    if (w == kWarpMma + 2 && l == 0) tma_store_wait_all();
     tc_fence_before();
     __syncthreads();
     if (w == kWarpProducer) tmem_dealloc(tmem, kTmemCols);
