@@ -58,6 +58,17 @@ int device_info(int dev, DeviceInfo* out) {
         }
         e = cudaFuncSetAttribute(gla::gla_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gla::kSmemBytes);
         if (e != cudaSuccess) { note_cuda("cudaFuncSetAttribute", e); return GLA_B200_ERR_CUDA; }
+        // The warpgroups of the kernel re-divide the registers the CTA was launched with (setmaxnreg); a group that
+        // asks for more than the others release would wait for ever, so the budgets are checked against what this
+        // build of the kernel really gets at launch.
+        cudaFuncAttributes fa;
+        e = cudaFuncGetAttributes(&fa, gla::gla_fwd_kernel);
+        if (e != cudaSuccess) { note_cuda("cudaFuncGetAttributes", e); return GLA_B200_ERR_CUDA; }
+        if (fa.numRegs * gla::kThreads < gla::kRegBudgetTotal) {
+            snprintf(g_cuda_err, sizeof(g_cuda_err), "kernel launches with %d registers per thread, its register budgets need %d",
+                     fa.numRegs, (gla::kRegBudgetTotal + gla::kThreads - 1) / gla::kThreads);
+            return GLA_B200_ERR_DEVICE;
+        }
         d.ok = true;
         d.sms = sms;
         d.attr_set = true;

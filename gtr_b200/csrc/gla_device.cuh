@@ -74,6 +74,14 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Per-warpgroup register budget: every warp of an aligned group of four executes the same instruction.
+template <int N> __device__ __forceinline__ void reg_alloc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void reg_dealloc() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ------------------------------------------------------------------ fences / named barriers
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -56,7 +56,6 @@ constexpr int kComputeWarps = GLA_COMPUTE_WARPS;
 constexpr int kComputeThreads = 32 * kComputeWarps;
 constexpr int kThreads = 2 * kComputeThreads + 128;  // + TMA producer, score-MMA issuer, output/state-MMA issuer, store warp
 constexpr int kRowsPerThread = kChunk / kComputeWarps;   // gate math: logical rows per thread
-constexpr int kColSplit = kComputeWarps / 4;
 constexpr int kTmemCols = 256;
 constexpr uint32_t kTmA = 0;              // scores: two buffers of 32 columns, each two interleaved halves
 constexpr uint32_t kTmOS = 64;            // two buffers of 64 columns: outputs (lane offset 0), state increment (lane offset 16)
@@ -130,14 +129,13 @@ struct Misc {
     // A barrier may run at most one phase ahead of its slowest waiter.  Barriers whose producer can run further
     // ahead are rings indexed like the resource they guard (stage, or tf32 buffer / score accumulator).
     uint64_t o_ready[2], o_free[2];
-    uint64_t ops_ready[kNumStages], a_done[2], a_free[2], a16_ready[2], os_done[2], os_free[2], s16_ready;
+    uint64_t ops_ready[kNumStages], a16_ready[kNumStages], a_done[2], a_free[2], os_done[2], os_free[2], s16_ready;
     uint32_t tmem_base;
     volatile uint32_t abort;
     int item;
     uint32_t wide[kSlots];
     alignas(16) float tot[2][kComputeWarps][kD];   // per-warp gate sums (float2 access), double-buffered
     alignas(16) float b4s[kSlots][kD]; // chunk totals G_L per channel
-    float ssq[2][kColSplit][kChunk];   // fused epilogue: per-row partial sums of squares, by chunk parity
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "misc block too large");
 
@@ -175,7 +173,7 @@ __device__ __forceinline__ void raise_timeout(const Ctx& c, uint32_t where) {
 #ifndef GLA_SPIN_SLEEP_NS
 #define GLA_SPIN_SLEEP_NS 0
 #endif
-__device__ __noinline__ void mbar_wait_slow(const Ctx& c, uint32_t b, uint32_t parity) {
+__device__ __forceinline__ void mbar_wait_slow(const Ctx& c, uint32_t b, uint32_t parity) {
     const uint64_t t0 = globaltimer_ns();
     uint32_t n = 0;
     while (true) {
@@ -198,9 +196,10 @@ __device__ __forceinline__ void mbar_wait(const Ctx& c, uint64_t* bar, uint32_t 
 
 // Wait of a whole warp group: its first warp polls the mbarrier, the others sleep in the hardware barrier
 // `bar_id` (a warp parked in bar.sync issues nothing, a polling warp competes with the working ones).
-__device__ __forceinline__ void group_wait(const Ctx& c, uint64_t* bar, uint32_t parity, int group_warp, uint32_t bar_id) {
+__device__ __forceinline__ void group_wait(const Ctx& c, uint64_t* bar, uint32_t parity, int group_warp, uint32_t bar_id,
+                                           uint32_t group_threads) {
     if (group_warp == 0) mbar_wait(c, bar, parity);
-    named_bar_sync(bar_id, kComputeThreads);
+    named_bar_sync(bar_id, group_threads);
 }
 
 // One arrival per warp: the lanes order their work before lane 0 with a warp barrier, lane 0 arrives for all of
@@ -503,12 +502,12 @@ __device__ __forceinline__ uint32_t sw_f16(uint32_t row, uint32_t col) {     // 
 
 // Exact intra-chunk scores for chunks whose gates are too strong for a common reference:
 // A[i][j] = sum_c q[i][c] k[j][c] 2^(G[i][c] - G[j][c]) for j at or before i along the scan.
-__device__ __noinline__ void exact_scores(const Ctx& c, uint8_t* a16_tile, const uint8_t* qkbuf, int tid) {
+__device__ __noinline__ void exact_scores(const Ctx& c, uint8_t* a16_tile, const uint8_t* qkbuf, int tid, int nthreads) {
     const bool rev = c.p->rev != 0;
     const uint8_t* gs = qkbuf;
     const uint8_t* qs = qkbuf + kOffKbarRel;
     const uint8_t* ks = qs + kTileBytes;
-    constexpr uint32_t kPerRow = kComputeThreads / kChunk;
+    const uint32_t kPerRow = static_cast<uint32_t>(nthreads) / kChunk;
     const uint32_t i = tid / kPerRow;
     for (uint32_t j = tid % kPerRow; j < 64; j += kPerRow) {
         float s = 0.f;
@@ -553,6 +552,22 @@ __device__ __forceinline__ void store_row_f16(uint32_t tile, uint32_t row, uint3
         st_shared_v4(a, pack_half2(x[8 * m], x[8 * m + 1]), pack_half2(x[8 * m + 2], x[8 * m + 3]),
                      pack_half2(x[8 * m + 4], x[8 * m + 5]), pack_half2(x[8 * m + 6], x[8 * m + 7]));
     }
+}
+
+// Causal mask along the scan on N score columns j0.. of query row rho (keep key j0 + j at or before the query;
+// at or after it for reversed scans), then the fp16 tile.  Branch-free selects: the two half-warps sit on
+// different sides of the diagonal.
+template <int N>
+__device__ __forceinline__ void mask_and_store_scores(bool rev, uint32_t a16, uint32_t rho, uint32_t j0, float* x) {
+    const int lim = static_cast<int>(rho) - static_cast<int>(j0);
+    if (!rev) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) x[j] = (j <= lim) ? x[j] : 0.f;
+    } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) x[j] = (j >= lim) ? x[j] : 0.f;
+    }
+    store_row_f16<N / 8>(a16, rho, j0 >> 3, x);
 }
 
 // Self-test of the bounded waits: one warp waits on an mbarrier nobody arrives at and on a global
@@ -605,19 +620,37 @@ __device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
     return it;
 }
 
-// Warp roles (one CTA per SM):
-//   warps 0..7   epilogue group TMEM read-out: scores -> fp16 tile, outputs -> tile -> TMA store, state in fp32
-//                               registers, look-back and publication of segment states
+// Warp roles (one CTA per SM, 20 warps in five warpgroups):
+//   warps 0..3   state group    TMEM read-out of outputs and state increments: state in fp32 registers (lanes
+//                               16-31: one state row each; lanes 0-15: one output row each), fp16 copy of the state
+//                               for the next chunk, output tile, look-back and publication of segment states
+//   warps 4..7   score group    TMEM read-out of the intra-chunk scores -> causal mask -> fp16 tile
 //   warps 8..15  gate group     raw q,k,g tiles -> qh, kh (fp16, in place) and qb, kb (tf32, two buffers)
 //   warp 16      TMA producer   warp 17  score MMAs   warp 18  output and state MMAs   warp 19  output TMA stores
-// The epilogue group is the serial chain of a sequence (state in, state out) and its code is one long
-// dependency chain; the gate group is throughput work with slack and plenty of independent instructions.
-// The warp scheduler favours the lower warp ids when several warps are ready, so the epilogue group takes them:
-// with the gate group first, epilogue instructions waited ~15 cycles each whenever the gate math was running.
-// (one thread needs ~100 cycles to issue a tcgen05.mma whatever its shape, so the 28 small MMAs of a chunk
-// are issued from two threads)
-// The gate group runs up to two chunks ahead of the epilogue group (bounded by the tf32 buffers), so operand
-// preparation of chunk i+1, i+2 overlaps the MMAs and epilogues of chunk i.
+// The chain from one chunk's state to the next (state group -> output MMAs -> state group) is the serial part of a
+// sequence, and everything on it is a dependent sequence of synchronising operations that cost tens of cycles each;
+// the score read-out is therefore a group of its own and overlaps it.  The gate group is throughput work and runs
+// up to two chunks ahead (bounded by the tf32 buffers).  Each warpgroup sets its own register budget (setmaxnreg):
+// the state group holds a 64-wide state row per thread, the four service warps need next to nothing.
+constexpr int kStateWarps = 4, kScoreWarps = 4;
+constexpr int kStateThreads = 32 * kStateWarps, kScoreThreads = 32 * kScoreWarps;
+static_assert(kStateWarps + kScoreWarps == kComputeWarps && kComputeWarps == 8, "warp layout");
+// Register budgets per thread of the five warpgroups.  setmaxnreg only re-divides what the CTA got at launch
+// (kThreads x the kernel's register count, 96 under these launch bounds), and an increase waits, without limit, until
+// the other groups have released enough: the budgets must not add up to more than that.
+#ifndef GLA_REGS_STATE
+#define GLA_REGS_STATE 160
+#define GLA_REGS_SCORE 64
+#define GLA_REGS_GATE 104
+#define GLA_REGS_SERVICE 48
+#endif
+constexpr int kRegsState = GLA_REGS_STATE, kRegsScore = GLA_REGS_SCORE, kRegsGate = GLA_REGS_GATE, kRegsService = GLA_REGS_SERVICE;
+constexpr int kLaunchRegs = 96;
+constexpr int kRegBudgetTotal = kStateThreads * kRegsState + kScoreThreads * kRegsScore + kComputeThreads * kRegsGate + 128 * kRegsService;
+#ifndef GLA_REGS_NOCHECK
+static_assert(kRegBudgetTotal <= kThreads * kLaunchRegs, "register budgets exceed what the CTA is launched with");
+#endif
+
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params P) {
     extern __shared__ uint8_t smem_raw[];
@@ -631,7 +664,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
 #ifdef GLA_TRACE
     uint32_t trace_n = 0;
 #endif
-    constexpr int kWarpProducer = 2 * kComputeWarps, kWarpMma = 2 * kComputeWarps + 1;
+    constexpr int kWarpGate = kStateWarps + kScoreWarps;
+    constexpr int kWarpProducer = kWarpGate + kComputeWarps, kWarpMma = kWarpProducer + 1;
 
     Ctx ctx;
     ctx.p = &P;
@@ -647,18 +681,18 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         for (int s = 0; s < kNumStages; ++s) {
             mbar_init(smem_u32(&M.full[s]), 1);
             mbar_init(smem_u32(&M.empty[s]), 1);
+            mbar_init(smem_u32(&M.ops_ready[s]), kComputeWarps);
+            mbar_init(smem_u32(&M.a16_ready[s]), kScoreWarps);
         }
-        for (int s = 0; s < kNumStages; ++s) mbar_init(smem_u32(&M.ops_ready[s]), kComputeWarps);
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&M.a_done[b]), 1);
-            mbar_init(smem_u32(&M.a_free[b]), kComputeWarps);
-            mbar_init(smem_u32(&M.a16_ready[b]), kComputeWarps);
+            mbar_init(smem_u32(&M.a_free[b]), kScoreWarps);
             mbar_init(smem_u32(&M.os_done[b]), 1);
-            mbar_init(smem_u32(&M.os_free[b]), kComputeWarps);
-            mbar_init(smem_u32(&M.o_ready[b]), kComputeWarps);
+            mbar_init(smem_u32(&M.os_free[b]), kStateWarps);
+            mbar_init(smem_u32(&M.o_ready[b]), kStateWarps);
             mbar_init(smem_u32(&M.o_free[b]), 1);
         }
-        mbar_init(smem_u32(&M.s16_ready), kComputeWarps);
+        mbar_init(smem_u32(&M.s16_ready), kStateWarps);
         M.abort = 0;
 #ifdef GLA_TRACE
         for (int i = 0; i < kSlots; ++i) M.wide[i] = 0;
@@ -677,223 +711,42 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     tc_fence_after();
     const uint32_t tmem = __shfl_sync(0xffffffffu, M.tmem_base, 0);
 
-    // Every role walks the same sequence of chunks and keeps its own counters:
+    // Every role walks the same sequence of work items and chunks and keeps its own counters:
     //   ctr  chunks seen so far (both passes): stage = ctr % kNumStages, exchange slot = ctr % kSlots
-    //   c2   output-pass chunks seen so far: tf32 buffer / score accumulator = c2 & 1
+    //   c2   output-pass chunks seen so far: tf32 buffer / score accumulator / output tile = c2 & 1
     uint32_t ctr = 0, c2 = 0;
-    uint32_t n_s16 = 0;   // single barrier: use count (output-MMA role)
-    uint32_t wide_hist = 0;   // gate group: bit b = the last chunk in tf32 buffer b took the exact path
-
-    while (true) {
+    // Work items come from a ticket counter; all roles fetch the same item at the same two block barriers.
+    auto next_item = [&]() -> int {
         if (tid == 0) M.item = static_cast<int>(atomicAdd(P.ctrl, 1u));
         __syncthreads();
-        const int item = __shfl_sync(0xffffffffu, M.item, 0);   // known to be warp-uniform
-        if (item >= P.num_items) break;
-        const ItemInfo it = decode_item(P, item);
-        const int npass = it.state_pass ? 2 : 1;
+        return __shfl_sync(0xffffffffu, M.item, 0);   // known to be warp-uniform
+    };
 
-        // The four service warps below run their loops with all 32 lanes, in warp-uniform control flow, and only the
-        // issue of an asynchronous instruction (TMA, tcgen05.mma, commit) is left to one elected lane.  Loop
-        // counters, descriptors and coordinates then live in uniform registers, which is what those instructions
-        // take; a loop run by a single lane inside a divergent branch pays a move from the vector registers per
-        // operand and needs three times as long per MMA.
-        if (w == kWarpProducer) {
-            // ------------------------------------------------------------ TMA producer
-            for (int pass = 0; pass < npass; ++pass) {
-                const bool state_only = it.state_pass && pass == 0;
-                BoxWalker bw(P, it.first_chunk * kChunk);
-                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                    const uint32_t s = ctr % kNumStages, n = ctr / kNumStages;
-                    mbar_wait(ctx, &M.empty[s], (n & 1u) ^ 1u);
-                    GLA_EV(30);
-                    if (elect_one()) {
-                        const int valid = chunk_valid((it.first_chunk + i) * kChunk, P.T);
-                        const int ntens = state_only ? 3 : 4;
-                        const uint32_t bar = smem_u32(&M.full[s]);
-                        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(valid * 128 * ntens));
-                        const uint32_t stage = base + kOffStage + s * kStageBytes;
-                        bw.for_each(P, [&](int id, int r, int c, int row) {
-                            const uint32_t off = static_cast<uint32_t>(row) * 128u;
-                            if (!state_only)
-                                tma_load_5d(stage + 0 * kTileBytes + off, &maps.m[TQ][id], bar, 0, it.h, r, c, it.b);
-                            tma_load_5d(stage + 1 * kTileBytes + off, &maps.m[TK][id], bar, 0, it.h, r, c, it.b);
-                            tma_load_5d(stage + 2 * kTileBytes + off, &maps.m[TG][id], bar, 0, it.h, r, c, it.b);
-                            tma_load_5d(stage + 3 * kTileBytes + off, &maps.m[TV][id], bar, 0, it.h, r, c, it.b);
-                        });
-                    }
-                    __syncwarp();
-                    bw.advance(P);
-                }
-            }
-        } else if (w == kWarpMma) {
-            // ------------------------------------------------------------ score MMAs (output pass only)
-            constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 32);
-            for (int pass = 0; pass < npass; ++pass) {
-                const bool state_only = it.state_pass && pass == 0;
-                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                    const uint32_t s = ctr % kNumStages, b = c2 & 1u;
-                    // a parity wait only tells apart consecutive phases, so this warp has to observe
-                    // every phase of the ring, also those of state-only chunks it has nothing to do for
-                    mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);
-                    if (state_only) continue;
-                    mbar_wait(ctx, &M.a_free[b], ((c2 >> 1) & 1u) ^ 1u);   // epilogue done with this buffer's previous use
-                    GLA_EV(20);
-                    tc_fence_after();
-                    const uint32_t wide = __shfl_sync(0xffffffffu, M.wide[ctr % kSlots], 0);
-                    if (elect_one()) {
-                        if (!wide && !GLA_DBGP(4)) {
-                            const uint64_t dQ = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes);
-                            const uint64_t dK = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes + kOffKbarRel);
-                            const uint32_t tmA = tmem + kTmA + 32u * b;
-#pragma unroll
-                            for (uint32_t ks = 0; ks < 8; ++ks) {
-                                const uint32_t o = ((ks >> 2) * kTileBytes + (ks & 3) * 32u) >> 4;
-                                umma_tf32(tmA, dQ + o, dK + o, idA, ks);
-                                umma_tf32(tmA + kLane16, dQ + o, dK + o + ((32 * 128) >> 4), idA, ks);
-                            }
-                        }
-                        umma_commit(smem_u32(&M.a_done[b]));
-                    }
-                    __syncwarp();
-                    GLA_EV(21);
-                    ++c2;
-                }
-            }
-        } else if (w == kWarpMma + 1) {
-            // ------------------------------------------------------------ output and state MMAs
-            constexpr uint32_t idO = umma_idesc(FMT_F16, 0, 1, 64, 64);
-            constexpr uint32_t idS = umma_idesc(FMT_F16, 1, 1, 64, 64);
-            const uint32_t tmO = tmem + kTmOS, tmS = tmem + kTmOS + kLane16;
-            const uint64_t dS16 = umma_desc_sw128(base + kOffS16, 8192);
-            for (int pass = 0; pass < npass; ++pass) {
-                const bool state_only = it.state_pass && pass == 0;
-                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                    const uint32_t s = ctr % kNumStages;
-                    const uint32_t stage = base + kOffStage + s * kStageBytes;
-                    const uint64_t dq = umma_desc_sw128(stage), dk = umma_desc_sw128(stage + kTileBytes, 8192),
-                                   da16 = umma_desc_sw128(stage + 2 * kTileBytes),
-                                   dv = umma_desc_sw128(stage + 3 * kTileBytes, 8192);
-                    // The O / state-increment accumulators are double-buffered: everything of this chunk that
-                    // does not need the incoming state (A.v and kh^T.v) is issued while the epilogue still works
-                    // on the previous chunk; only the read-out qh.S waits for the state, so the serial chain
-                    // from one chunk's state to the next is one short MMA group.
-                    const uint32_t p = ctr & 1u;
-                    const uint32_t tmOp = tmO + 64u * p, tmSp = tmS + 64u * p;
-                    mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);          // v arrives by TMA
-                    mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);     // qh, kh written in place
-                    mbar_wait(ctx, &M.os_free[p], ((ctr >> 1) & 1u) ^ 1u);        // epilogue has read this buffer's previous use
-                    GLA_EV(22);
-                    if (!state_only) mbar_wait(ctx, &M.a16_ready[c2 & 1u], (c2 >> 1) & 1u);
-                    GLA_EV(23);
-                    tc_fence_after();
-                    if (elect_one() && !GLA_DBGP(5)) {
-                        if (!state_only) {
-#pragma unroll
-                            for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmOp, da16 + ks * 2u, dv + ks * 128u, idO, ks);
-                        }
-#pragma unroll
-                        for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmSp, dk + ks * 128u, dv + ks * 128u, idS, ks);
-                    }
-                    __syncwarp();
-                    if (!state_only) {
-                        mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
-                        tc_fence_after();
-                        ++c2;
-                    }
-                    if (elect_one()) {
-                        if (!state_only && !GLA_DBGP(5)) {
-#pragma unroll
-                            for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmOp, dq + ks * 2u, dS16 + ks * 128u, idO, 1);
-                        }
-                        umma_commit(smem_u32(&M.os_done[p]));
-                        // the same completion hands the stage back to the producer: gate math and the score MMAs are
-                        // long done with it, and nothing reads it after these MMAs
-                        umma_commit(smem_u32(&M.empty[s]));
-                    }
-                    __syncwarp();
-                    GLA_EV(24);
-                }
-            }
-        } else if (w == kWarpMma + 2) {
-            // ------------------------------------------------------------ store warp
-            // sends finished output tiles out by TMA (two tiles, so the epilogue of one chunk overlaps the store of
-            // the previous one)
-            for (int pass = 0; pass < npass; ++pass) {
-                if (it.state_pass && pass == 0) continue;
-                BoxWalker bw(P, it.first_chunk * kChunk);
-                for (int i = 0; i < it.nchunks; ++i, ++c2) {
-                    const uint32_t j = c2 & 1u;
-                    mbar_wait(ctx, &M.o_ready[j], (c2 >> 1) & 1u);
-                    if (elect_one()) {
-                        const uint32_t tile = base + kOffOut + j * kTileBytes;
-                        bw.for_each(P, [&](int id, int r, int c, int row) {
-                            tma_store_5d(&maps.m[TO][id], tile + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
-                        });
-                        tma_store_commit();
-                        tma_store_wait_read();
-                        mbar_arrive(smem_u32(&M.o_free[j]));
-                    }
-                    __syncwarp();
-                    bw.advance(P);
-                }
-            }
-        } else if (w >= kComputeWarps) {
-            // ------------------------------------------------------------ gate group
-            const int gw = w - kComputeWarps;
-            for (int pass = 0; pass < npass; ++pass) {
-                const bool state_only = it.state_pass && pass == 0;
-                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                    const uint32_t s = ctr % kNumStages;
-                    mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);
-                    uint32_t qbar = 0;
-                    uint64_t* buf_bar = nullptr;
-                    uint32_t buf_parity = 0;
-                    if (!state_only) {
-                        const uint32_t b = c2 & 1u;
-                        // the buffer is free once the score MMAs of its previous use have completed (a_done); if that
-                        // use stashed operands for the exact path, once the epilogue has read them (a_free)
-                        buf_bar = ((wide_hist >> b) & 1u) ? &M.a_free[b] : &M.a_done[b];
-                        buf_parity = ((c2 >> 1) & 1u) ^ 1u;
-                        qbar = base + kOffQbar + b * kQkBufBytes;
-                    }
-                    GLA_EV(12);
-                    const bool was_wide = GLA_DBGP(0) ? false :
-                        gate_math(ctx, base + kOffStage + s * kStageBytes, qbar, static_cast<int>(ctr),
-                                  chunk_valid((it.first_chunk + i) * kChunk, P.T), gw, l, state_only, buf_bar, buf_parity);
-                    if (!state_only) {
-                        const uint32_t b = c2 & 1u;
-                        wide_hist = (wide_hist & ~(1u << b)) | ((was_wide ? 1u : 0u) << b);
-                        ++c2;
-                    }
-                    warp_arrive(&M.ops_ready[s], l);
-                    GLA_EV(13);
-                }
-            }
-        } else {
-            // ------------------------------------------------------------ epilogue group
-            // State ownership: lanes 16-31 of epilogue warp e hold, in fp32, columns [kSc*ch, kSc*ch+kSc) of
-            // state row (channel) my_c = 16*(e&3) + (l&15), ch = e>>2; lanes 0-15 hold the same columns of
-            // output row 16*(e&3) + l.
-            constexpr int kSc = kD / kColSplit;       // O / state columns per thread
-            constexpr int kAc = 32 / kColSplit;       // score columns per thread (per 32-column half)
-            const int e = w, etid = tid;
-            const bool owner = l >= 16;
-            const int quad = e & 3, ch = e >> 2;
-            const int my_c = 16 * quad + (l & 15);
-            const int col0 = kSc * ch;
-            const uint32_t rho = 16 * quad + (l & 15);
-            const size_t srow = (static_cast<size_t>(it.seq) * kD + my_c) * kD + col0;   // this thread's part of a state row
+    if (w < kStateWarps) {
+        // ==================================================================== state group
+        reg_alloc<kRegsState>();
+        const int etid = tid;
+        const bool owner = l >= 16;
+        const int quad = w;
+        const int my_c = 16 * quad + (l & 15);          // state row (channel) of lanes 16-31
+        const uint32_t rho = 16 * quad + (l & 15);      // output row of lanes 0-15
+        float S[kD];
+        while (true) {
+            const int item = next_item();
+            if (item >= P.num_items) break;
+            const ItemInfo it = decode_item(P, item);
+            const int npass = it.state_pass ? 2 : 1;
+            const size_t srow = (static_cast<size_t>(it.seq) * kD + my_c) * kD;   // this thread's state row
             const size_t slot = static_cast<size_t>(it.seq) * P.NS + it.seg;
-            float S[kSc];
             float gsum = 0.f;       // log2 of the segment's total decay for channel my_c
 
             auto load_initial = [&]() {
 #pragma unroll
-                for (int x = 0; x < kSc; ++x) S[x] = 0.f;
+                for (int x = 0; x < kD; ++x) S[x] = 0.f;
                 if (owner && P.s0 != nullptr) {
                     const float4* src = reinterpret_cast<const float4*>(P.s0 + srow);
 #pragma unroll
-                    for (int x = 0; x < kSc / 4; ++x) {
+                    for (int x = 0; x < kD / 4; ++x) {
                         const float4 v4 = __ldg(src + x);
                         S[4 * x] = v4.x; S[4 * x + 1] = v4.y; S[4 * x + 2] = v4.z; S[4 * x + 3] = v4.w;
                     }
@@ -903,51 +756,12 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                 if (owner) {
                     float4* dst = reinterpret_cast<float4*>(dst_row);
 #pragma unroll
-                    for (int x4 = 0; x4 < kSc / 4; ++x4)
+                    for (int x4 = 0; x4 < kD / 4; ++x4)
                         dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
                 }
                 __threadfence();
-                named_bar_sync(2, kComputeThreads);
+                named_bar_sync(2, kStateThreads);
                 if (etid == 0) st_release_gpu(P.flags + slot, flag_value);
-            };
-            // scores of the output-pass chunk with running indices (cc, k2): TMEM -> causal mask -> fp16 tile
-            // (takes the place of the raw gate tile of its stage)
-            auto scores = [&](uint32_t cc, uint32_t k2) {
-                const uint32_t s = cc % kNumStages, b = k2 & 1u;
-                const uint32_t a16 = base + kOffStage + s * kStageBytes + 2 * kTileBytes;
-                group_wait(ctx, &M.a_done[b], (k2 >> 1) & 1u, e, 2);
-                GLA_EV(10);
-                tc_fence_after();
-                if (GLA_DBGP(2)) {
-                    warp_arrive(&M.a_free[b], l);
-                } else if (!M.wide[cc % kSlots]) {
-                    float x[kAc];
-                    tmem_row<kAc>(tmem, quad, kTmA + 32u * b + kAc * ch, x);
-                    GLA_EV(50);
-                    tc_fence_before();
-                    warp_arrive(&M.a_free[b], l);
-                    GLA_EV(54);
-                    const uint32_t j0 = (l >> 4) * 32u + kAc * ch;   // lanes 16-31 hold key rows 32-63
-                    // causal mask along the scan: keep key j0 + j at or before query rho (after it, reversed);
-                    // branch-free selects -- the two half-warps sit on different sides of the diagonal
-                    const int lim = static_cast<int>(rho) - static_cast<int>(j0);
-                    if (!P.rev) {
-#pragma unroll
-                        for (int j = 0; j < kAc; ++j) x[j] = (j <= lim) ? x[j] : 0.f;
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < kAc; ++j) x[j] = (j >= lim) ? x[j] : 0.f;
-                    }
-                    GLA_EV(55);
-                    store_row_f16<kAc / 8>(a16, rho, j0 >> 3, x);
-                    GLA_EV(51);
-                } else {
-                    exact_scores(ctx, base_ptr + (a16 - base), base_ptr + kOffQbar + b * kQkBufBytes, etid);
-                    warp_arrive(&M.a_free[b], l);
-                }
-                fence_proxy_async_smem();
-                warp_arrive(&M.a16_ready[b], l);
-                GLA_EV(11);
             };
 
             for (int pass = 0; pass < npass; ++pass) {
@@ -957,14 +771,14 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     if (it.seg == 0) load_initial();
                     else {
 #pragma unroll
-                        for (int x = 0; x < kSc; ++x) S[x] = 0.f;
+                        for (int x = 0; x < kD; ++x) S[x] = 0.f;
                     }
                 } else {
                     if (it.seg == 0) load_initial();
                     else {
                         // decoupled look-back: S <- state entering this segment
 #pragma unroll
-                        for (int x = 0; x < kSc; ++x) S[x] = 0.f;
+                        for (int x = 0; x < kD; ++x) S[x] = 0.f;
                         float dlog = 0.f;
                         int j = it.seg - 1;
                         const uint64_t t0 = globaltimer_ns();
@@ -985,12 +799,12 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             const bool inclusive = __all_sync(0xffffffffu, f == 2u);
                             if (gave_up) break;   // result undefined, status word set
                             const float dacc = ex2(dlog);
-                            const float* src_row = inclusive ? P.incl + sj * (kD * kD) + my_c * kD + col0
-                                                             : P.agg + sj * kAggStride + my_c * kD + col0;
+                            const float* src_row = inclusive ? P.incl + sj * (kD * kD) + my_c * kD
+                                                             : P.agg + sj * kAggStride + my_c * kD;
                             if (owner) {
                                 const float4* src = reinterpret_cast<const float4*>(src_row);
 #pragma unroll
-                                for (int x4 = 0; x4 < kSc / 4; ++x4) {
+                                for (int x4 = 0; x4 < kD / 4; ++x4) {
                                     const float4 v4 = __ldcg(src + x4);
                                     S[4 * x4] = fmaf(dacc, v4.x, S[4 * x4]);
                                     S[4 * x4 + 1] = fmaf(dacc, v4.y, S[4 * x4 + 1]);
@@ -1007,29 +821,28 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             // inclusive state after this segment = decay * incoming + increment
                             if (owner) {
                                 const float dseg = ex2(gsum);
-                                const float4* inc = reinterpret_cast<const float4*>(P.agg + slot * kAggStride + my_c * kD + col0);
-                                float4* dst = reinterpret_cast<float4*>(P.incl + slot * (kD * kD) + my_c * kD + col0);
+                                const float4* inc = reinterpret_cast<const float4*>(P.agg + slot * kAggStride + my_c * kD);
+                                float4* dst = reinterpret_cast<float4*>(P.incl + slot * (kD * kD) + my_c * kD);
 #pragma unroll
-                                for (int x4 = 0; x4 < kSc / 4; ++x4) {
+                                for (int x4 = 0; x4 < kD / 4; ++x4) {
                                     const float4 a4 = __ldcg(inc + x4);
                                     dst[x4] = make_float4(fmaf(dseg, S[4 * x4], a4.x), fmaf(dseg, S[4 * x4 + 1], a4.y),
                                                           fmaf(dseg, S[4 * x4 + 2], a4.z), fmaf(dseg, S[4 * x4 + 3], a4.w));
                                 }
                             }
                             __threadfence();
-                            named_bar_sync(2, kComputeThreads);
+                            named_bar_sync(2, kStateThreads);
                             if (etid == 0) st_release_gpu(P.flags + slot, 2u);
                         }
                     }
-                    if (owner) store_row_f16<kSc / 8>(base + kOffS16, rho, col0 >> 3, S);
+                    if (owner) store_row_f16<kD / 8>(base + kOffS16, rho, 0, S);
                     fence_proxy_async_smem();
                     warp_arrive(&M.s16_ready, l);
-                    scores(ctr, c2);
                 }
 
                 // position along the scan of this thread's output row in the pass's first chunk: u, and for
                 // column scans its column cc and row rr inside the column (floor division: u < 0 only for rows
-                // before the start of a reversed ragged chunk, which are never written)
+                // before the start of a reversed ragged chunk, which are never written); fused epilogue only
                 int u = 0, rr = 0, cc = 0;
                 if (!state_only && P.gated) {
                     const int p0 = it.first_chunk * kChunk;
@@ -1041,58 +854,42 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     }
                 }
                 for (int i = 0; i < it.nchunks; ++i, ++ctr) {
-                    if (!state_only) {
-                        if (i + 1 < it.nchunks) scores(ctr + 1, c2 + 1);   // overlaps the output/state MMAs of chunk i
-                        ++c2;
-                    }
-                    // lanes 0-15: outputs -> scale -> fp16 -> global memory
+                    // lanes 0-15: output row -> fp16 output tile
                     // lanes 16-31: S <- 2^(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
                     const uint32_t p = ctr & 1u;
-                    group_wait(ctx, &M.os_done[p], (ctr >> 1) & 1u, e, 2);
+                    group_wait(ctx, &M.os_done[p], (ctr >> 1) & 1u, w, 2, kStateThreads);
                     GLA_EV(14);
                     tc_fence_after();
                     // the exchange slot's chunk total first: its latency hides behind the TMEM read
                     const float b4 = ld_shared_f(smem_u32(&M.b4s[ctr % kSlots][my_c]));
-                    if (GLA_DBGP(3)) {
-                        warp_arrive(&M.os_free[p], l);
-                    } else {
-                        float x[kSc];
-                        tmem_row<kSc>(tmem, quad, kTmOS + 64u * p + col0, x);
-                        GLA_EV(52);
-                        tc_fence_before();
-                        warp_arrive(&M.os_free[p], l);
-                        const float dec = owner ? ex2(b4) : 0.f;
-                        if (owner) gsum += b4;
+                    const float dec = owner ? ex2(b4) : 0.f;
+                    if (owner) gsum += b4;
 #pragma unroll
-                        for (int v = 0; v < kSc; ++v) S[v] = fmaf(dec, S[v], x[v]);   // lanes 0-15: dec = 0, S is the output row
+                    for (int hb = 0; hb < 2; ++hb) {        // two halves of 32 columns keep the register need bounded
+                        float x[32];
+                        tmem_row<32>(tmem, quad, kTmOS + 64u * p + 32u * hb, x);
+#pragma unroll
+                        for (int v = 0; v < 32; ++v)        // lanes 0-15: dec = 0, S is the output row
+                            S[32 * hb + v] = fmaf(dec, S[32 * hb + v], x[v]);
                     }
-                    if (!state_only && GLA_DBGP(3)) {
-                        const uint32_t j = (c2 - 1u) & 1u;
-                        mbar_wait(ctx, &M.o_free[j], (((c2 - 1u) >> 1) & 1u) ^ 1u);
-                        if (i + 1 < it.nchunks) warp_arrive(&M.s16_ready, l);
-                        warp_arrive(&M.o_ready[j], l);
-                    } else if (!state_only) {
+                    GLA_EV(52);
+                    tc_fence_before();
+                    warp_arrive(&M.os_free[p], l);
+                    if (!state_only) {
                         if (P.gated) {
-                            // y = o * rsqrt(mean(o^2) + eps) * w * silu(gate); a row's 64 columns are split over
-                            // kColSplit warps, which exchange their partial sums of squares through shared memory
-                            float ss = 0.f;
-#pragma unroll
-                            for (int v = 0; v < kSc; ++v) ss = fmaf(S[v], S[v], ss);
-                            const int par = ctr & 1u;
-                            if (!owner) M.ssq[par][ch][rho] = ss * (P.o_mul * P.o_mul);
-                            named_bar_sync(2, kComputeThreads);
-                            // token read at this row of the chunk (same mapping as the TMA boxes)
+                            // y = o * rsqrt(mean(o^2) + eps) * w * silu(gate) on the output rows (lanes 0-15);
+                            // the token read at this row of the chunk follows the same mapping as the TMA boxes
                             if (!owner && u >= 0 && u < P.T) {
-                                float tot = 0.f;
+                                float ss = 0.f;
 #pragma unroll
-                                for (int cc2 = 0; cc2 < kColSplit; ++cc2) tot += M.ssq[par][cc2][rho];
-                                const float rinv = P.o_mul * rsqrtf(tot * (1.f / kD) + P.rms_eps);
+                                for (int v = 0; v < kD; ++v) ss = fmaf(S[v], S[v], ss);
+                                const float rinv = P.o_mul * rsqrtf(ss * (P.o_mul * P.o_mul) * (1.f / kD) + P.rms_eps);
                                 const long long tok = (P.Wc > 1) ? static_cast<long long>(rr) * P.Wc + cc : u;
                                 const uint4* gp = reinterpret_cast<const uint4*>(
-                                    P.gate + it.b * P.gate_sb + tok * P.gate_st + it.h * P.gate_sh + col0);
-                                const uint4* wp = reinterpret_cast<const uint4*>(P.rms_w + col0);
+                                    P.gate + it.b * P.gate_sb + tok * P.gate_st + it.h * P.gate_sh);
+                                const uint4* wp = reinterpret_cast<const uint4*>(P.rms_w);
 #pragma unroll
-                                for (int m = 0; m < kSc / 8; ++m) {
+                                for (int m = 0; m < kD / 8; ++m) {
                                     const uint4 g4 = __ldg(gp + m), w4 = __ldg(wp + m);
                                     const uint32_t gu[4] = {g4.x, g4.y, g4.z, g4.w}, wu[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
@@ -1116,17 +913,20 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         } else if (P.o_mul != 1.f) {      // scale not folded into q (zero, negative or not finite)
                             const float mul = owner ? 1.f : P.o_mul;
 #pragma unroll
-                            for (int v = 0; v < kSc; ++v) S[v] *= mul;
+                            for (int v = 0; v < kD; ++v) S[v] *= mul;
                         }
                         // lanes 16-31: fp16 copy of the new state for the next chunk's read-out;
-                        // lanes 0-15: output row into an output tile (the store warp sends it out); c2 already counts
-                        // this chunk
-                        const uint32_t j = (c2 - 1u) & 1u;
-                        mbar_wait(ctx, &M.o_free[j], (((c2 - 1u) >> 1) & 1u) ^ 1u);   // tile's previous store has read it
-                        store_row_f16<kSc / 8>(owner ? base + kOffS16 : base + kOffOut + j * kTileBytes, rho, col0 >> 3, S);
+                        // lanes 0-15: output row into an output tile (the store warp sends it out)
+                        const uint32_t j = c2 & 1u;
+                        mbar_wait(ctx, &M.o_free[j], ((c2 >> 1) & 1u) ^ 1u);   // tile's previous store has read it
+                        store_row_f16<kD / 8>(owner ? base + kOffS16 : base + kOffOut + j * kTileBytes, rho, 0, S);
                         fence_proxy_async_smem();
-                        if (i + 1 < it.nchunks) warp_arrive(&M.s16_ready, l);
-                        warp_arrive(&M.o_ready[j], l);
+                        __syncwarp();
+                        if (l == 0) {
+                            if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.s16_ready));
+                            mbar_arrive(smem_u32(&M.o_ready[j]));
+                        }
+                        ++c2;
                         GLA_EV(15);
                     }
                     GLA_EV(16);
@@ -1134,24 +934,263 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
 
                 if (state_only) {
                     if (it.seg == 0) {
-                        publish(P.incl + slot * (kD * kD) + my_c * kD + col0, 2u);
+                        publish(P.incl + slot * (kD * kD) + my_c * kD, 2u);
                     } else {
-                        if (owner && ch == 0) P.agg[slot * kAggStride + kD * kD + my_c] = gsum;
-                        publish(P.agg + slot * kAggStride + my_c * kD + col0, 1u);
+                        if (owner) P.agg[slot * kAggStride + kD * kD + my_c] = gsum;
+                        publish(P.agg + slot * kAggStride + my_c * kD, 1u);
                     }
                 }
             }
             if (it.seg == P.NS - 1 && P.sT != nullptr && owner) {
                 float4* dst = reinterpret_cast<float4*>(P.sT + srow);
 #pragma unroll
-                for (int x4 = 0; x4 < kSc / 4; ++x4)
+                for (int x4 = 0; x4 < kD / 4; ++x4)
                     dst[x4] = make_float4(S[4 * x4], S[4 * x4 + 1], S[4 * x4 + 2], S[4 * x4 + 3]);
             }
+            __syncthreads();   // the item is drained
         }
-        __syncthreads();   // the item is drained: every role restarts from the same counters
+    } else if (w < kWarpGate) {
+        // ==================================================================== score group
+        // scores of the output-pass chunks: TMEM -> causal mask -> fp16 tile (takes the place of the raw gate tile
+        // of the chunk's stage).  Thread: query row 16*quad + (lane & 15), key columns 32*(lane >> 4) .. +31.
+        reg_dealloc<kRegsScore>();
+        const int quad = w - kStateWarps, stid = tid - kStateThreads;
+        const uint32_t rho = 16 * quad + (l & 15);
+        const uint32_t j0 = (l >> 4) * 32u;
+        while (true) {
+            const int item = next_item();
+            if (item >= P.num_items) break;
+            const ItemInfo it = decode_item(P, item);
+            const int npass = it.state_pass ? 2 : 1;
+            for (int pass = 0; pass < npass; ++pass) {
+                if (it.state_pass && pass == 0) {
+                    ctr += it.nchunks;
+                    continue;
+                }
+                for (int i = 0; i < it.nchunks; ++i, ++ctr, ++c2) {
+                    const uint32_t s = ctr % kNumStages, b = c2 & 1u;
+                    const uint32_t a16 = base + kOffStage + s * kStageBytes + 2 * kTileBytes;
+                    group_wait(ctx, &M.a_done[b], (c2 >> 1) & 1u, quad, 3, kScoreThreads);
+                    GLA_EV(10);
+                    tc_fence_after();
+                    if (!M.wide[ctr % kSlots]) {
+                        float x[32];
+                        tmem_row<32>(tmem, quad, kTmA + 32u * b, x);
+                        tc_fence_before();
+                        warp_arrive(&M.a_free[b], l);
+                        mask_and_store_scores<32>(P.rev != 0, a16, rho, j0, x);
+                    } else {
+                        exact_scores(ctx, base_ptr + (a16 - base), base_ptr + kOffQbar + b * kQkBufBytes, stid, kScoreThreads);
+                        warp_arrive(&M.a_free[b], l);
+                    }
+                    fence_proxy_async_smem();
+                    warp_arrive(&M.a16_ready[c2 % kNumStages], l);
+                    GLA_EV(11);
+                }
+            }
+            __syncthreads();
+        }
+    } else if (w < kWarpProducer) {
+        // ==================================================================== gate group
+        reg_alloc<kRegsGate>();
+        const int gw = w - kWarpGate;
+        uint32_t wide_hist = 0;   // bit b = the last chunk in tf32 buffer b took the exact path
+        while (true) {
+            const int item = next_item();
+            if (item >= P.num_items) break;
+            const ItemInfo it = decode_item(P, item);
+            const int npass = it.state_pass ? 2 : 1;
+            for (int pass = 0; pass < npass; ++pass) {
+                const bool state_only = it.state_pass && pass == 0;
+                for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                    const uint32_t s = ctr % kNumStages;
+                    mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);
+                    uint32_t qbar = 0;
+                    uint64_t* buf_bar = nullptr;
+                    uint32_t buf_parity = 0;
+                    if (!state_only) {
+                        const uint32_t b = c2 & 1u;
+                        // the buffer is free once the score MMAs of its previous use have completed (a_done); if that
+                        // use stashed operands for the exact path, once the score group has read them (a_free)
+                        buf_bar = ((wide_hist >> b) & 1u) ? &M.a_free[b] : &M.a_done[b];
+                        buf_parity = ((c2 >> 1) & 1u) ^ 1u;
+                        qbar = base + kOffQbar + b * kQkBufBytes;
+                    }
+                    GLA_EV(12);
+                    const bool was_wide = GLA_DBGP(0) ? false :
+                        gate_math(ctx, base + kOffStage + s * kStageBytes, qbar, static_cast<int>(ctr),
+                                  chunk_valid((it.first_chunk + i) * kChunk, P.T), gw, l, state_only, buf_bar, buf_parity);
+                    if (!state_only) {
+                        const uint32_t b = c2 & 1u;
+                        wide_hist = (wide_hist & ~(1u << b)) | ((was_wide ? 1u : 0u) << b);
+                        ++c2;
+                    }
+                    warp_arrive(&M.ops_ready[s], l);
+                    GLA_EV(13);
+                }
+            }
+            __syncthreads();
+        }
+    } else {
+        // ==================================================================== service warps
+        // These four warps run their loops with all 32 lanes, in warp-uniform control flow, and only the issue of
+        // an asynchronous instruction (TMA, tcgen05.mma, commit) is left to one elected lane.  Loop counters,
+        // descriptors and coordinates then live in uniform registers, which is what those instructions take; a loop
+        // run by a single lane inside a divergent branch pays a move from the vector registers per operand and
+        // needs three times as long per MMA.
+        reg_dealloc<kRegsService>();
+        uint32_t n_s16 = 0;   // single barrier: use count (output-MMA role)
+        while (true) {
+            const int item = next_item();
+            if (item >= P.num_items) break;
+            const ItemInfo it = decode_item(P, item);
+            const int npass = it.state_pass ? 2 : 1;
+            if (w == kWarpProducer) {
+                // ------------------------------------------------------------ TMA producer
+                for (int pass = 0; pass < npass; ++pass) {
+                    const bool state_only = it.state_pass && pass == 0;
+                    BoxWalker bw(P, it.first_chunk * kChunk);
+                    for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                        const uint32_t s = ctr % kNumStages, n = ctr / kNumStages;
+                        mbar_wait(ctx, &M.empty[s], (n & 1u) ^ 1u);
+                        GLA_EV(30);
+                        if (elect_one()) {
+                            const int valid = chunk_valid((it.first_chunk + i) * kChunk, P.T);
+                            const int ntens = state_only ? 3 : 4;
+                            const uint32_t bar = smem_u32(&M.full[s]);
+                            mbar_arrive_expect_tx(bar, static_cast<uint32_t>(valid * 128 * ntens));
+                            const uint32_t stage = base + kOffStage + s * kStageBytes;
+                            bw.for_each(P, [&](int id, int r, int c, int row) {
+                                const uint32_t off = static_cast<uint32_t>(row) * 128u;
+                                if (!state_only)
+                                    tma_load_5d(stage + 0 * kTileBytes + off, &maps.m[TQ][id], bar, 0, it.h, r, c, it.b);
+                                tma_load_5d(stage + 1 * kTileBytes + off, &maps.m[TK][id], bar, 0, it.h, r, c, it.b);
+                                tma_load_5d(stage + 2 * kTileBytes + off, &maps.m[TG][id], bar, 0, it.h, r, c, it.b);
+                                tma_load_5d(stage + 3 * kTileBytes + off, &maps.m[TV][id], bar, 0, it.h, r, c, it.b);
+                            });
+                        }
+                        __syncwarp();
+                        bw.advance(P);
+                    }
+                }
+            } else if (w == kWarpMma) {
+                // ------------------------------------------------------------ score MMAs (output pass only)
+                constexpr uint32_t idA = umma_idesc(FMT_TF32, 0, 0, 64, 32);
+                for (int pass = 0; pass < npass; ++pass) {
+                    const bool state_only = it.state_pass && pass == 0;
+                    for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                        const uint32_t s = ctr % kNumStages, b = c2 & 1u;
+                        // a parity wait only tells apart consecutive phases, so this warp has to observe
+                        // every phase of the ring, also those of state-only chunks it has nothing to do for
+                        mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);
+                        if (state_only) continue;
+                        mbar_wait(ctx, &M.a_free[b], ((c2 >> 1) & 1u) ^ 1u);   // score group done with this buffer's previous use
+                        GLA_EV(20);
+                        tc_fence_after();
+                        const uint32_t wide = __shfl_sync(0xffffffffu, M.wide[ctr % kSlots], 0);
+                        if (elect_one()) {
+                            if (!wide && !GLA_DBGP(4)) {
+                                const uint64_t dQ = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes);
+                                const uint64_t dK = umma_desc_sw128(base + kOffQbar + b * kQkBufBytes + kOffKbarRel);
+                                const uint32_t tmA = tmem + kTmA + 32u * b;
+#pragma unroll
+                                for (uint32_t ks = 0; ks < 8; ++ks) {
+                                    const uint32_t o = ((ks >> 2) * kTileBytes + (ks & 3) * 32u) >> 4;
+                                    umma_tf32(tmA, dQ + o, dK + o, idA, ks);
+                                    umma_tf32(tmA + kLane16, dQ + o, dK + o + ((32 * 128) >> 4), idA, ks);
+                                }
+                            }
+                            umma_commit(smem_u32(&M.a_done[b]));
+                        }
+                        __syncwarp();
+                        GLA_EV(21);
+                        ++c2;
+                    }
+                }
+            } else if (w == kWarpMma + 1) {
+                // ------------------------------------------------------------ output and state MMAs
+                constexpr uint32_t idO = umma_idesc(FMT_F16, 0, 1, 64, 64);
+                constexpr uint32_t idS = umma_idesc(FMT_F16, 1, 1, 64, 64);
+                const uint32_t tmO = tmem + kTmOS, tmS = tmem + kTmOS + kLane16;
+                const uint64_t dS16 = umma_desc_sw128(base + kOffS16, 8192);
+                for (int pass = 0; pass < npass; ++pass) {
+                    const bool state_only = it.state_pass && pass == 0;
+                    for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                        const uint32_t s = ctr % kNumStages;
+                        const uint32_t stage = base + kOffStage + s * kStageBytes;
+                        const uint64_t dq = umma_desc_sw128(stage), dk = umma_desc_sw128(stage + kTileBytes, 8192),
+                                       da16 = umma_desc_sw128(stage + 2 * kTileBytes),
+                                       dv = umma_desc_sw128(stage + 3 * kTileBytes, 8192);
+                        // The O / state-increment accumulators are double-buffered: everything of this chunk that
+                        // does not need the incoming state (A.v and kh^T.v) is issued while the state group still
+                        // works on the previous chunk; only the read-out qh.S waits for the state, so the serial
+                        // chain from one chunk's state to the next is one short MMA group.
+                        const uint32_t p = ctr & 1u;
+                        const uint32_t tmOp = tmO + 64u * p, tmSp = tmS + 64u * p;
+                        mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);          // v arrives by TMA
+                        mbar_wait(ctx, &M.ops_ready[s], (ctr / kNumStages) & 1u);     // qh, kh written in place
+                        mbar_wait(ctx, &M.os_free[p], ((ctr >> 1) & 1u) ^ 1u);        // state group has read this buffer's previous use
+                        GLA_EV(22);
+                        if (!state_only) mbar_wait(ctx, &M.a16_ready[c2 % kNumStages], (c2 / kNumStages) & 1u);
+                        GLA_EV(23);
+                        tc_fence_after();
+                        if (elect_one() && !GLA_DBGP(5)) {
+                            if (!state_only) {
+#pragma unroll
+                                for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmOp, da16 + ks * 2u, dv + ks * 128u, idO, ks);
+                            }
+#pragma unroll
+                            for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmSp, dk + ks * 128u, dv + ks * 128u, idS, ks);
+                        }
+                        __syncwarp();
+                        if (!state_only) {
+                            mbar_wait(ctx, &M.s16_ready, n_s16++ & 1u);
+                            tc_fence_after();
+                            ++c2;
+                        }
+                        if (elect_one()) {
+                            if (!state_only && !GLA_DBGP(5)) {
+#pragma unroll
+                                for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmOp, dq + ks * 2u, dS16 + ks * 128u, idO, 1);
+                            }
+                            umma_commit(smem_u32(&M.os_done[p]));
+                            // the same completion hands the stage back to the producer: gate math and the score MMAs
+                            // are long done with it, and nothing reads it after these MMAs
+                            umma_commit(smem_u32(&M.empty[s]));
+                        }
+                        __syncwarp();
+                        GLA_EV(24);
+                    }
+                }
+            } else {
+                // ------------------------------------------------------------ store warp
+                // sends finished output tiles out by TMA (two tiles, so the state group's work on one chunk overlaps
+                // the store of the previous one)
+                for (int pass = 0; pass < npass; ++pass) {
+                    if (it.state_pass && pass == 0) continue;
+                    BoxWalker bw(P, it.first_chunk * kChunk);
+                    for (int i = 0; i < it.nchunks; ++i, ++c2) {
+                        const uint32_t j = c2 & 1u;
+                        mbar_wait(ctx, &M.o_ready[j], (c2 >> 1) & 1u);
+                        if (elect_one()) {
+                            const uint32_t tile = base + kOffOut + j * kTileBytes;
+                            bw.for_each(P, [&](int id, int r, int c, int row) {
+                                tma_store_5d(&maps.m[TO][id], tile + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
+                            });
+                            tma_store_commit();
+                            tma_store_wait_read();
+                            mbar_arrive(smem_u32(&M.o_free[j]));
+                        }
+                        __syncwarp();
+                        bw.advance(P);
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        if (w == kWarpMma + 2 && elect_one()) tma_store_wait_all();
     }
 
-    if (w == kWarpMma + 2 && l == 0) tma_store_wait_all();
     tc_fence_before();
     __syncthreads();
     if (w == kWarpProducer) tmem_dealloc(tmem, kTmemCols);
