@@ -44,18 +44,14 @@ constexpr int kStageBytes = 4 * kTileBytes;
 #ifndef GLA_STAGES
 #define GLA_STAGES 4
 #endif
-#ifndef GLA_COMPUTE_WARPS
-#define GLA_COMPUTE_WARPS 8
-#endif
 constexpr int kCtasPerSm = GLA_MIN_CTAS;    // resident CTAs per SM the launch bounds and the grid size assume
 constexpr int kNumStages = GLA_STAGES;
-// Two groups of kComputeWarps warps each: the gate group (operand preparation) and the epilogue group
-// (TMEM read-out, state).  In the epilogue group kComputeWarps/4 warps share a TMEM lane quadrant and
-// split its columns.
-constexpr int kComputeWarps = GLA_COMPUTE_WARPS;
-constexpr int kComputeThreads = 32 * kComputeWarps;
-constexpr int kThreads = 2 * kComputeThreads + 128;  // + TMA producer, score-MMA issuer, output/state-MMA issuer, store warp
-constexpr int kRowsPerThread = kChunk / kComputeWarps;   // gate math: logical rows per thread
+// Five warpgroups of four warps: state group, score group, two gate teams, service warps.
+constexpr int kStateWarps = 4, kScoreWarps = 4, kTeamWarps = 4, kGateTeams = 2, kGateWarps = kTeamWarps * kGateTeams;
+constexpr int kStateThreads = 32 * kStateWarps, kScoreThreads = 32 * kScoreWarps, kTeamThreads = 32 * kTeamWarps,
+              kGateThreads = 32 * kGateWarps;
+constexpr int kGateGroups = 8;               // gate math: row groups of eight rows, two per warp of a team
+constexpr int kThreads = kStateThreads + kScoreThreads + kGateThreads + 128;
 constexpr int kTmemCols = 256;
 constexpr uint32_t kTmA = 0;              // scores: two buffers of 32 columns, each two interleaved halves
 constexpr uint32_t kTmOS = 64;            // two buffers of 64 columns: outputs (lane offset 0), state increment (lane offset 16)
@@ -120,7 +116,7 @@ constexpr int kOffKbarRel = 2 * kTileBytes;              // kb inside a buffer
 constexpr int kOffS16 = kOffQbar + 2 * kQkBufBytes;
 constexpr int kOffOut = kOffS16 + kTileBytes;            // two output tiles (fp16, swizzled), sent out by the store warp
 constexpr int kOffMisc = kOffOut + 2 * kTileBytes;
-constexpr int kMiscBytes = 4096 + 512 * kComputeWarps;
+constexpr int kMiscBytes = 8192;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + alignment slack
 
 struct Misc {
@@ -134,7 +130,7 @@ struct Misc {
     volatile uint32_t abort;
     int item;
     uint32_t wide[kSlots];
-    alignas(16) float tot[2][kComputeWarps][kD];   // per-warp gate sums (float2 access), double-buffered
+    alignas(16) float tot[2][kGateGroups][kD];     // gate sums per row group (float4 access), double-buffered
     alignas(16) float b4s[kSlots][kD]; // chunk totals G_L per channel
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "misc block too large");
@@ -270,7 +266,7 @@ __device__ __forceinline__ void sts64(uint32_t a, float x, float y) { st_shared_
 // logsigmoid(x) / normalizer, before the gate math reads it.  Kept out of line and rolled: it is
 // a rarely used mode and must not bloat the main loop.
 __device__ __noinline__ void logits_to_log_gates(uint8_t* tg, float inv_norm, int tid) {
-    for (int e = tid; e < kChunk * kD / 2; e += kComputeThreads) {
+    for (int e = tid; e < kChunk * kD / 2; e += kTeamThreads) {
         uint32_t* p = reinterpret_cast<uint32_t*>(tg) + e;
         const float2 x = unpack_half2(*p);
         *p = pack_half2_sat(logsigmoid_f(x.x) * inv_norm, logsigmoid_f(x.y) * inv_norm);
@@ -284,82 +280,94 @@ __device__ __noinline__ void logits_to_log_gates(uint8_t* tg, float inv_norm, in
 #define GLA_DBG(bit) 0
 #define GLA_DBGP(bit) 0
 #endif
-// Gate math for one chunk (all compute threads).  Thread (w, l) owns logical rows
-// 8w..8w+7 and channels 2l, 2l+1.  Logical row = position inside the chunk along the scan;
-// the physical (shared-memory / TMEM) row is mirrored for reversed scans.  Tiles are rows of
-// 128 bytes whose 16-byte units are XOR-swizzled with (row & 7); since 8w is a multiple of 8
-// the swizzle of logical row i depends on i only, which is a compile-time constant here.
+// Gate math for one chunk (the four warps of one gate team; `bar_id` is the team's named barrier).  Thread (w, l) owns the eight logical rows
+// 16w + 8(l>>4) .. +7 (row group 2w + (l>>4)) and the four channels 4(l&15) .. +3, so that every access is a
+// 64-bit (fp16 tiles) or 128-bit (tf32 tiles, exchange rows) shared-memory instruction.  Logical row =
+// position inside the chunk along the scan; the physical (shared-memory / TMEM) row is mirrored for reversed
+// scans.  Tiles are rows of 128 bytes whose 16-byte units are XOR-swizzled with (row & 7); a thread's first row
+// is a multiple of 8, so the swizzle of its i-th row depends on i only, a compile-time constant here.
 //
 // The hot variants (full chunk, tf32 path) are straight-line code without branches between rows, so
-// that the eight independent rows can be interleaved by the instruction scheduler; ragged chunks
+// that the independent rows can be interleaved by the instruction scheduler; ragged chunks
 // and chunks on the exact path take out-of-line rolled versions.
 struct GateLane {
-    uint32_t a16;    // byte offset of (logical row 8w, channel 2l) in an fp16 tile, without the swizzle term
+    uint32_t a16;    // byte offset of (first logical row, first channel) in an fp16 tile, without the swizzle term
     uint32_t a32;    // same for the two-half tf32 tiles
-    uint32_t x16;    // swizzle term (16-byte unit index << 4) of logical row 8w, fp16 tiles
+    uint32_t x16;    // swizzle term (16-byte unit index << 4) of the first row, fp16 tiles
     uint32_t x32;    // same, tf32 tiles
 };
 template <bool kRev>
 __device__ __forceinline__ GateLane gate_lane(int w, int l) {
     GateLane g;
-    constexpr uint32_t R = kRowsPerThread;
-    const uint32_t first = R * w;                                   // first logical row of this thread
+    const uint32_t cg = l & 15u;                                    // channel group: channels 4cg .. 4cg+3
+    const uint32_t first = 16u * w + 8u * (l >> 4);                 // first logical row, a multiple of 8
     const uint32_t row0 = kRev ? (63u - first) : first;
-    // (physical row & 7) of logical row first + i is ((first & 7) + i) forward and 7 - that reversed; R
-    // divides 8, so (first & 7) and i < R occupy different bits and the sum is an XOR
-    const uint32_t rbits = (first & 7u) ^ (kRev ? 7u : 0u);
-    g.a16 = row0 * 128u + ((l & 3u) << 2);
-    g.a32 = row0 * 128u + (l >> 4) * kTileBytes + ((l & 1u) << 3);
-    g.x16 = ((l >> 2) ^ rbits) << 4;
-    g.x32 = (((l & 15u) >> 1) ^ rbits) << 4;
+    // (physical row & 7) of logical row first + i is i forward and 7 - i = 7 ^ i reversed
+    const uint32_t rbits = kRev ? 7u : 0u;
+    g.a16 = row0 * 128u + ((cg & 1u) << 3);
+    g.a32 = row0 * 128u + (cg >> 3) * kTileBytes;
+    g.x16 = ((cg >> 1) ^ rbits) << 4;
+    g.x32 = ((cg & 7u) ^ rbits) << 4;
     return g;
 }
-// offsets of logical row 8w + i (i is a compile-time constant at every use)
+// offsets of the thread's i-th row (i is a compile-time constant at every use in the hot path)
 template <bool kRev> __device__ __forceinline__ uint32_t off16(const GateLane& g, int i) {
     return (kRev ? g.a16 - 128u * i : g.a16 + 128u * i) + (g.x16 ^ (static_cast<uint32_t>(i) << 4));
 }
 template <bool kRev> __device__ __forceinline__ uint32_t off32(const GateLane& g, int i) {
     return (kRev ? g.a32 - 128u * i : g.a32 + 128u * i) + (g.x32 ^ (static_cast<uint32_t>(i) << 4));
 }
+__device__ __forceinline__ void unpack4(uint2 r, float* x) {
+    const float2 a = unpack_half2(r.x), b = unpack_half2(r.y);
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+}
+
+struct Gate4 { float v[4]; };
 
 // Rolled, out-of-line row pass for the rare cases: a ragged last chunk (rows past `valid` are zeroed)
 // and chunks on the exact-score path (`wide`: G and raw q, k are stashed in plain layouts where the
 // tf32 operands would go).  Recomputes the running gate sum from the (still raw) gate tile.
 template <bool kRev>
 __device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, uint32_t qbar, int valid, int w, int l,
-                                               bool state_only, bool wide, float off0, float off1, float b40, float b41, float e10,
-                                               float e11, float e20, float e21) {
+                                               bool state_only, bool wide, Gate4 off, Gate4 b4, Gate4 e1, Gate4 e2) {
     const float qx = c.p->q_exp;
     const GateLane gl = gate_lane<kRev>(w, l);
     const uint32_t tq = stage, tk = stage + kTileBytes, tg = stage + 2 * kTileBytes, tv = stage + 3 * kTileBytes;
     const uint32_t kbar = qbar + kOffKbarRel;
-    const uint32_t c0 = 2u * l;
-    float a0 = off0, a1 = off1;
+    const uint32_t c0 = 4u * (l & 15u);
+    const int first = 16 * w + 8 * (l >> 4);
+    float a[4] = {off.v[0], off.v[1], off.v[2], off.v[3]};
 #pragma unroll 1
-    for (int i = 0; i < kRowsPerThread; ++i) {
+    for (int i = 0; i < 8; ++i) {
         const uint32_t o16 = (kRev ? gl.a16 - 128u * i : gl.a16 + 128u * i) + (gl.x16 ^ (static_cast<uint32_t>(i) << 4));
         const uint32_t o32 = (kRev ? gl.a32 - 128u * i : gl.a32 + 128u * i) + (gl.x32 ^ (static_cast<uint32_t>(i) << 4));
-        const bool live = kRowsPerThread * w + i < valid;
-        const float2 gv = unpack_half2(lds32(tg + o16));
-        a0 += live ? gv.x * kLog2e : 0.f;
-        a1 += live ? gv.y * kLog2e : 0.f;
-        const uint32_t kr = live ? lds32(tk + o16) : 0u;
-        const uint32_t qr = (live && !state_only) ? lds32(tq + o16) : 0u;
-        const float2 kv = unpack_half2(kr), qv = unpack_half2(qr);
-        const float kh0 = kv.x * ex2(b40 - a0), kh1 = kv.y * ex2(b41 - a1);
-        sts32(tk + o16, pack_half2_sat(kh0, kh1));
-        if (!live) sts32(tv + o16, 0u);                // rows past the end must be finite for the MMAs
+        const bool live = first + i < valid;
+        float gv[4], kv[4], qv[4], kh[4], qh[4];
+        unpack4(ld_shared_v2(tg + o16), gv);
+        const uint2 kr = live ? ld_shared_v2(tk + o16) : make_uint2(0u, 0u);
+        const uint2 qr = (live && !state_only) ? ld_shared_v2(tq + o16) : make_uint2(0u, 0u);
+        unpack4(kr, kv);
+        unpack4(qr, qv);
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+            a[ch] += live ? gv[ch] * kLog2e : 0.f;
+            kh[ch] = kv[ch] * ex2(b4.v[ch] - a[ch]);
+            qh[ch] = qv[ch] * ex2(a[ch] + qx);
+        }
+        st_shared_v2(tk + o16, pack_half2_sat(kh[0], kh[1]), pack_half2_sat(kh[2], kh[3]));
+        if (!live) st_shared_v2(tv + o16, 0u, 0u);                // rows past the end must be finite for the MMAs
         if (!state_only) {
-            const float qh0 = qv.x * ex2(a0 + qx), qh1 = qv.y * ex2(a1 + qx);
-            sts32(tq + o16, pack_half2_sat(qh0, qh1));
+            st_shared_v2(tq + o16, pack_half2_sat(qh[0], qh[1]), pack_half2_sat(qh[2], qh[3]));
             if (!wide) {
-                sts64(qbar + o32, round_tf32(qh0 * e10), round_tf32(qh1 * e11));
-                sts64(kbar + o32, round_tf32(kh0 * e20), round_tf32(kh1 * e21));
+                st_shared_f4(qbar + o32, round_tf32(qh[0] * e1.v[0]), round_tf32(qh[1] * e1.v[1]),
+                             round_tf32(qh[2] * e1.v[2]), round_tf32(qh[3] * e1.v[3]));
+                st_shared_f4(kbar + o32, round_tf32(kh[0] * e2.v[0]), round_tf32(kh[1] * e2.v[1]),
+                             round_tf32(kh[2] * e2.v[2]), round_tf32(kh[3] * e2.v[3]));
             } else {   // plain layouts: G fp32 [64][64] at qbar; raw q, k fp16 [64][64] at kbar
-                const int rho = kRev ? 63 - (kRowsPerThread * w + i) : kRowsPerThread * w + i;
-                sts64(qbar + rho * 256 + c0 * 4, a0, a1);
-                sts32(kbar + rho * 128 + c0 * 2, qr);
-                sts32(kbar + kTileBytes + rho * 128 + c0 * 2, kr);
+                const int rho = kRev ? 63 - (first + i) : first + i;
+                st_shared_f4(qbar + rho * 256 + c0 * 4, a[0], a[1], a[2], a[3]);
+                st_shared_v2(kbar + rho * 128 + c0 * 2, qr.x, qr.y);
+                st_shared_v2(kbar + kTileBytes + rho * 128 + c0 * 2, kr.x, kr.y);
             }
         }
     }
@@ -367,114 +375,126 @@ __device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, uin
 
 template <bool kStateOnly, bool kRev>
 __device__ __forceinline__ bool gate_math_t(const Ctx& c, uint32_t stage, uint32_t qbar, int n, int valid, int w, int l,
-                                            uint64_t* buf_bar, uint32_t buf_parity) {
-    constexpr int R = kRowsPerThread;
-    static_assert(R == 8 || R == 4, "the swizzle shortcut needs a row count that divides 8");
+                                            uint64_t* buf_bar, uint32_t buf_parity, uint32_t bar_id) {
+    constexpr int R = 8;
     const Params& P = *c.p;
     Misc& M = *c.misc;
     const int par = n & 1, slot = n % kSlots;
     const GateLane gl = gate_lane<kRev>(w, l);
     const uint32_t tq = stage, tk = stage + kTileBytes, tg = stage + 2 * kTileBytes;
     const uint32_t kbar = qbar + kOffKbarRel;
-    const uint32_t c0 = 2u * l;
-    const uint32_t tot_sa = smem_u32(&M.tot[par][0][c0]);   // + ww * kD * 4
+    const uint32_t c0 = 4u * (l & 15u);
+    const int grp = 2 * w + (l >> 4);                        // row group (eight rows) of this thread
+    const uint32_t tot_sa = smem_u32(&M.tot[par][0][c0]);   // + group * kD * 4
     const bool ragged = valid < kChunk;
 
     GLA_EVC(c, 45);
     if (P.inv_norm > 0.f) {
         logits_to_log_gates(c.base + (tg - c.smem), P.inv_norm, 32 * w + l);
-        named_bar_sync(1, kComputeThreads);
+        named_bar_sync(bar_id, kTeamThreads);
     }
-    uint32_t graw[R], kraw[R], qraw[R];
+    uint2 graw[R], kraw[R], qraw[R];
 #pragma unroll
-    for (int i = 0; i < R; ++i) graw[i] = lds32(tg + off16<kRev>(gl, i));
+    for (int i = 0; i < R; ++i) graw[i] = ld_shared_v2(tg + off16<kRev>(gl, i));
     if (!ragged) {
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            kraw[i] = lds32(tk + off16<kRev>(gl, i));
-            if (!kStateOnly) qraw[i] = lds32(tq + off16<kRev>(gl, i));
+            kraw[i] = ld_shared_v2(tk + off16<kRev>(gl, i));
+            if (!kStateOnly) qraw[i] = ld_shared_v2(tq + off16<kRev>(gl, i));
         }
     }
     GLA_EVC(c, 44);
-    float cs0[R], cs1[R];
+    float cs[R][4];
     {
-        float a0 = 0.f, a1 = 0.f;
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
         if (!ragged) {
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                const float2 gv = unpack_half2(graw[i]);
-                a0 = fmaf(gv.x, kLog2e, a0);
-                a1 = fmaf(gv.y, kLog2e, a1);
-                cs0[i] = a0;
-                cs1[i] = a1;
+                float gv[4];
+                unpack4(graw[i], gv);
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    a[ch] = fmaf(gv[ch], kLog2e, a[ch]);
+                    cs[i][ch] = a[ch];
+                }
             }
         } else {
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                const float2 gv = unpack_half2(graw[i]);
-                const bool live = R * w + i < valid;
-                a0 += live ? gv.x * kLog2e : 0.f;
-                a1 += live ? gv.y * kLog2e : 0.f;
-                cs0[i] = a0;
-                cs1[i] = a1;
+                float gv[4];
+                unpack4(graw[i], gv);
+                const bool live = 16 * w + 8 * (l >> 4) + i < valid;
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    a[ch] += live ? gv[ch] * kLog2e : 0.f;
+                    cs[i][ch] = a[ch];
+                }
             }
         }
-        sts64(tot_sa + w * kD * 4, a0, a1);
+        st_shared_f4(tot_sa + grp * kD * 4, a[0], a[1], a[2], a[3]);
     }
     GLA_EVC(c, 40);
     // the tf32 buffer written below is free once the score MMAs of its previous use have completed; one warp
     // polls for that, the exchange barrier tells the others
     if (!kStateOnly && w == 0) mbar_wait(c, buf_bar, buf_parity);
-    named_bar_sync(1, kComputeThreads);
+    named_bar_sync(bar_id, kTeamThreads);
     GLA_EVC(c, 41);
-    float off0 = 0.f, off1 = 0.f, b40 = 0.f, b41 = 0.f, gm0 = 0.f, gm1 = 0.f;
+    Gate4 off, b4, gm;
 #pragma unroll
-    for (int ww = 0; ww < kComputeWarps; ++ww) {
-        const float2 t = ld_shared_f2(tot_sa + ww * kD * 4);
-        if (ww < w) { off0 += t.x; off1 += t.y; }
-        if (ww < kComputeWarps / 2) { gm0 += t.x; gm1 += t.y; }
-        b40 += t.x;
-        b41 += t.y;
+    for (int ch = 0; ch < 4; ++ch) off.v[ch] = b4.v[ch] = gm.v[ch] = 0.f;
+#pragma unroll
+    for (int g = 0; g < kGateGroups; ++g) {
+        const float4 t4 = ld_shared_f4(tot_sa + g * kD * 4);
+        const float t[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+            if (g < grp) off.v[ch] += t[ch];
+            if (g == kGateGroups / 2) gm.v[ch] = b4.v[ch];      // sum of the first half: the mid-chunk reference
+            b4.v[ch] += t[ch];
+        }
     }
-    if (w == 0) sts64(smem_u32(&M.b4s[slot][c0]), b40, b41);
+    if (grp == 0) st_shared_f4(smem_u32(&M.b4s[slot][c0]), b4.v[0], b4.v[1], b4.v[2], b4.v[3]);
     bool wide = false;
-    float e10 = 0.f, e11 = 0.f, e20 = 0.f, e21 = 0.f;
+    Gate4 e1, e2;
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) e1.v[ch] = e2.v[ch] = 0.f;
     if (!kStateOnly) {
-        wide = __any_sync(0xffffffffu, (-b40 > kWideLimit) || (-b41 > kWideLimit));
+        wide = __any_sync(0xffffffffu, (-b4.v[0] > kWideLimit) || (-b4.v[1] > kWideLimit) || (-b4.v[2] > kWideLimit) ||
+                                           (-b4.v[3] > kWideLimit));
         if (w == 0 && l == 0) M.wide[slot] = wide ? 1u : 0u;
-        e10 = ex2(-gm0);
-        e11 = ex2(-gm1);
-        e20 = ex2(gm0 - b40);
-        e21 = ex2(gm1 - b41);
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+            e1.v[ch] = ex2(-gm.v[ch]);
+            e2.v[ch] = ex2(gm.v[ch] - b4.v[ch]);
+        }
     }
     if (ragged || wide) {
-        gate_rows_general<kRev>(c, stage, qbar, valid, w, l, kStateOnly, wide, off0, off1, b40, b41, e10, e11, e20, e21);
+        gate_rows_general<kRev>(c, stage, qbar, valid, w, l, kStateOnly, wide, off, b4, e1, e2);
     } else {
-        // straight-line: exponents first, then products, then stores
-        const float ck0 = b40 - off0, ck1 = b41 - off1;
-        const float oq0 = off0 + P.q_exp, oq1 = off1 + P.q_exp;
-        float ek0[R], ek1[R], eq0[R], eq1[R];
+        float ck[4], oq[4];
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-            ek0[i] = ex2(ck0 - cs0[i]);
-            ek1[i] = ex2(ck1 - cs1[i]);
-            if (!kStateOnly) {
-                eq0[i] = ex2(oq0 + cs0[i]);
-                eq1[i] = ex2(oq1 + cs1[i]);
-            }
+        for (int ch = 0; ch < 4; ++ch) {
+            ck[ch] = b4.v[ch] - off.v[ch];
+            oq[ch] = off.v[ch] + P.q_exp;
         }
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            const float2 kv = unpack_half2(kraw[i]);
-            const float kh0 = kv.x * ek0[i], kh1 = kv.y * ek1[i];
-            sts32(tk + off16<kRev>(gl, i), pack_half2(kh0, kh1));
+            float kv[4], kh[4];
+            unpack4(kraw[i], kv);
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) kh[ch] = kv[ch] * ex2(ck[ch] - cs[i][ch]);
+            st_shared_v2(tk + off16<kRev>(gl, i), pack_half2(kh[0], kh[1]), pack_half2(kh[2], kh[3]));
             if (!kStateOnly) {
-                const float2 qv = unpack_half2(qraw[i]);
-                const float qh0 = qv.x * eq0[i], qh1 = qv.y * eq1[i];
-                sts32(tq + off16<kRev>(gl, i), pack_half2(qh0, qh1));
+                float qv[4], qh[4];
+                unpack4(qraw[i], qv);
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) qh[ch] = qv[ch] * ex2(oq[ch] + cs[i][ch]);
+                st_shared_v2(tq + off16<kRev>(gl, i), pack_half2(qh[0], qh[1]), pack_half2(qh[2], qh[3]));
                 if (!GLA_DBG(1)) {
-                    sts64(qbar + off32<kRev>(gl, i), round_tf32(qh0 * e10), round_tf32(qh1 * e11));
-                    sts64(kbar + off32<kRev>(gl, i), round_tf32(kh0 * e20), round_tf32(kh1 * e21));
+                    st_shared_f4(qbar + off32<kRev>(gl, i), round_tf32(qh[0] * e1.v[0]), round_tf32(qh[1] * e1.v[1]),
+                                 round_tf32(qh[2] * e1.v[2]), round_tf32(qh[3] * e1.v[3]));
+                    st_shared_f4(kbar + off32<kRev>(gl, i), round_tf32(kh[0] * e2.v[0]), round_tf32(kh[1] * e2.v[1]),
+                                 round_tf32(kh[2] * e2.v[2]), round_tf32(kh[3] * e2.v[3]));
                 }
             }
         }
@@ -487,13 +507,13 @@ __device__ __forceinline__ bool gate_math_t(const Ctx& c, uint32_t stage, uint32
 
 // Returns whether the chunk took the exact-score path (always false for state-only chunks).
 __device__ __forceinline__ bool gate_math(const Ctx& c, uint32_t stage, uint32_t qbar, int n, int valid, int w, int l,
-                                          bool state_only, uint64_t* buf_bar, uint32_t buf_parity) {
+                                          bool state_only, uint64_t* buf_bar, uint32_t buf_parity, uint32_t bar_id) {
     if (c.p->rev) {
-        if (state_only) return gate_math_t<true, true>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity);
-        return gate_math_t<false, true>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity);
+        if (state_only) return gate_math_t<true, true>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity, bar_id);
+        return gate_math_t<false, true>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity, bar_id);
     }
-    if (state_only) return gate_math_t<true, false>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity);
-    return gate_math_t<false, false>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity);
+    if (state_only) return gate_math_t<true, false>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity, bar_id);
+    return gate_math_t<false, false>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity, bar_id);
 }
 
 __device__ __forceinline__ uint32_t sw_f16(uint32_t row, uint32_t col) {     // col in fp16 elements
@@ -625,28 +645,26 @@ __device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
 //                               16-31: one state row each; lanes 0-15: one output row each), fp16 copy of the state
 //                               for the next chunk, output tile, look-back and publication of segment states
 //   warps 4..7   score group    TMEM read-out of the intra-chunk scores -> causal mask -> fp16 tile
-//   warps 8..15  gate group     raw q,k,g tiles -> qh, kh (fp16, in place) and qb, kb (tf32, two buffers)
+//   warps 8..15  gate group     raw q,k,g tiles -> qh, kh (fp16, in place) and qb, kb (tf32, two buffers); two
+//                               teams of four warps that take the chunks in turn
 //   warp 16      TMA producer   warp 17  score MMAs   warp 18  output and state MMAs   warp 19  output TMA stores
 // The chain from one chunk's state to the next (state group -> output MMAs -> state group) is the serial part of a
 // sequence, and everything on it is a dependent sequence of synchronising operations that cost tens of cycles each;
 // the score read-out is therefore a group of its own and overlaps it.  The gate group is throughput work and runs
 // up to two chunks ahead (bounded by the tf32 buffers).  Each warpgroup sets its own register budget (setmaxnreg):
 // the state group holds a 64-wide state row per thread, the four service warps need next to nothing.
-constexpr int kStateWarps = 4, kScoreWarps = 4;
-constexpr int kStateThreads = 32 * kStateWarps, kScoreThreads = 32 * kScoreWarps;
-static_assert(kStateWarps + kScoreWarps == kComputeWarps && kComputeWarps == 8, "warp layout");
 // Register budgets per thread of the five warpgroups.  setmaxnreg only re-divides what the CTA got at launch
 // (kThreads x the kernel's register count, 96 under these launch bounds), and an increase waits, without limit, until
 // the other groups have released enough: the budgets must not add up to more than that.
 #ifndef GLA_REGS_STATE
-#define GLA_REGS_STATE 160
+#define GLA_REGS_STATE 152
 #define GLA_REGS_SCORE 64
-#define GLA_REGS_GATE 104
-#define GLA_REGS_SERVICE 48
+#define GLA_REGS_GATE 112
+#define GLA_REGS_SERVICE 40
 #endif
 constexpr int kRegsState = GLA_REGS_STATE, kRegsScore = GLA_REGS_SCORE, kRegsGate = GLA_REGS_GATE, kRegsService = GLA_REGS_SERVICE;
 constexpr int kLaunchRegs = 96;
-constexpr int kRegBudgetTotal = kStateThreads * kRegsState + kScoreThreads * kRegsScore + kComputeThreads * kRegsGate + 128 * kRegsService;
+constexpr int kRegBudgetTotal = kStateThreads * kRegsState + kScoreThreads * kRegsScore + kGateThreads * kRegsGate + 128 * kRegsService;
 #ifndef GLA_REGS_NOCHECK
 static_assert(kRegBudgetTotal <= kThreads * kLaunchRegs, "register budgets exceed what the CTA is launched with");
 #endif
@@ -665,7 +683,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     uint32_t trace_n = 0;
 #endif
     constexpr int kWarpGate = kStateWarps + kScoreWarps;
-    constexpr int kWarpProducer = kWarpGate + kComputeWarps, kWarpMma = kWarpProducer + 1;
+    constexpr int kWarpProducer = kWarpGate + kGateWarps, kWarpMma = kWarpProducer + 1;
 
     Ctx ctx;
     ctx.p = &P;
@@ -681,7 +699,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         for (int s = 0; s < kNumStages; ++s) {
             mbar_init(smem_u32(&M.full[s]), 1);
             mbar_init(smem_u32(&M.empty[s]), 1);
-            mbar_init(smem_u32(&M.ops_ready[s]), kComputeWarps);
+            mbar_init(smem_u32(&M.ops_ready[s]), kTeamWarps);
             mbar_init(smem_u32(&M.a16_ready[s]), kScoreWarps);
         }
         for (int b = 0; b < 2; ++b) {
@@ -992,9 +1010,13 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         }
     } else if (w < kWarpProducer) {
         // ==================================================================== gate group
+        // Two teams of four warps take the chunks in turn (team = chunk parity), each on its own named barrier and
+        // its own exchange rows: a team works on a chunk for two chunk periods, and the two teams' instruction
+        // streams fill each other's stalls.
         reg_alloc<kRegsGate>();
         const int gw = w - kWarpGate;
-        uint32_t wide_hist = 0;   // bit b = the last chunk in tf32 buffer b took the exact path
+        const int team = gw / kTeamWarps, tw = gw % kTeamWarps;
+        const uint32_t bar_id = team ? 4u : 1u;
         while (true) {
             const int item = next_item();
             if (item >= P.num_items) break;
@@ -1003,28 +1025,19 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             for (int pass = 0; pass < npass; ++pass) {
                 const bool state_only = it.state_pass && pass == 0;
                 for (int i = 0; i < it.nchunks; ++i, ++ctr) {
+                    const uint32_t b = c2 & 1u, k2 = c2;
+                    if (!state_only) ++c2;
+                    if (static_cast<int>(ctr & 1u) != team) continue;
                     const uint32_t s = ctr % kNumStages;
                     mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);
-                    uint32_t qbar = 0;
-                    uint64_t* buf_bar = nullptr;
-                    uint32_t buf_parity = 0;
-                    if (!state_only) {
-                        const uint32_t b = c2 & 1u;
-                        // the buffer is free once the score MMAs of its previous use have completed (a_done); if that
-                        // use stashed operands for the exact path, once the score group has read them (a_free)
-                        buf_bar = ((wide_hist >> b) & 1u) ? &M.a_free[b] : &M.a_done[b];
-                        buf_parity = ((c2 >> 1) & 1u) ^ 1u;
-                        qbar = base + kOffQbar + b * kQkBufBytes;
-                    }
+                    // the tf32 buffer is free once the score group is done with its previous use (scores read from
+                    // TMEM, or the operands stashed for the exact path read from the buffer itself)
+                    const uint32_t qbar = state_only ? 0u : base + kOffQbar + b * kQkBufBytes;
                     GLA_EV(12);
-                    const bool was_wide = GLA_DBGP(0) ? false :
+                    if (!GLA_DBGP(0))
                         gate_math(ctx, base + kOffStage + s * kStageBytes, qbar, static_cast<int>(ctr),
-                                  chunk_valid((it.first_chunk + i) * kChunk, P.T), gw, l, state_only, buf_bar, buf_parity);
-                    if (!state_only) {
-                        const uint32_t b = c2 & 1u;
-                        wide_hist = (wide_hist & ~(1u << b)) | ((was_wide ? 1u : 0u) << b);
-                        ++c2;
-                    }
+                                  chunk_valid((it.first_chunk + i) * kChunk, P.T), tw, l, state_only, &M.a_free[b],
+                                  ((k2 >> 1) & 1u) ^ 1u, bar_id);
                     warp_arrive(&M.ops_ready[s], l);
                     GLA_EV(13);
                 }
