@@ -393,16 +393,9 @@ __device__ __forceinline__ bool gate_math_t(const Ctx& c, uint32_t stage, uint32
         logits_to_log_gates(c.base + (tg - c.smem), P.inv_norm, 32 * w + l);
         named_bar_sync(bar_id, kTeamThreads);
     }
-    uint2 graw[R], kraw[R], qraw[R];
+    uint2 graw[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) graw[i] = ld_shared_v2(tg + off16<kRev>(gl, i));
-    if (!ragged) {
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            kraw[i] = ld_shared_v2(tk + off16<kRev>(gl, i));
-            if (!kStateOnly) qraw[i] = ld_shared_v2(tq + off16<kRev>(gl, i));
-        }
-    }
     GLA_EVC(c, 44);
     float cs[R][4];
     {
@@ -480,13 +473,14 @@ __device__ __forceinline__ bool gate_math_t(const Ctx& c, uint32_t stage, uint32
 #pragma unroll
         for (int i = 0; i < R; ++i) {
             float kv[4], kh[4];
-            unpack4(kraw[i], kv);
+            unpack4(ld_shared_v2(tk + off16<kRev>(gl, i)), kv);   // k and q rows are read where they are used:
+                                                                  // held across the barrier they cost 32 registers
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) kh[ch] = kv[ch] * ex2(ck[ch] - cs[i][ch]);
             st_shared_v2(tk + off16<kRev>(gl, i), pack_half2(kh[0], kh[1]), pack_half2(kh[2], kh[3]));
             if (!kStateOnly) {
                 float qv[4], qh[4];
-                unpack4(qraw[i], qv);
+                unpack4(ld_shared_v2(tq + off16<kRev>(gl, i)), qv);
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) qh[ch] = qv[ch] * ex2(oq[ch] + cs[i][ch]);
                 st_shared_v2(tq + off16<kRev>(gl, i), pack_half2(qh[0], qh[1]), pack_half2(qh[2], qh[3]));
