@@ -210,10 +210,11 @@ __device__ __forceinline__ float ex2(float x) {   // 2^x, one MUFU op; results b
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// Round to the 10-bit tf32 mantissa (nearest, ties away) with two integer ops; kind::tf32 reads
-// only the upper 19 bits of each operand, so unrounded values would be truncated.
+// Round to the 10-bit tf32 mantissa (nearest, ties away) with one integer add: kind::tf32 reads only the upper
+// 19 bits of each operand, so adding half a unit of the last kept bit before that truncation rounds to nearest.
+// (Unrounded values would be truncated, which biases every product low.)
 __device__ __forceinline__ float round_tf32(float x) {
-    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+    return __uint_as_float(__float_as_uint(x) + 0x1000u);
 }
 // two floats -> packed fp16 pair, round to nearest.  One instruction; values beyond the fp16 range
 // become infinities, as with the reference kernels' conversions (a saturating conversion costs

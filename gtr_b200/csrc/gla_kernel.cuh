@@ -102,8 +102,11 @@ struct Params {
 // debug builds: lane 0 of every warp of CTA 0 appends (clock << 8 | event) to its own region, no atomics
 #define GLA_EV(id) do { if (blockIdx.x == 0 && !(P.dbg & 128) && (threadIdx.x & 31) == 0 && trace_n < 4096u) { \
         P.trace[(threadIdx.x >> 5) * 4096u + trace_n++] = ((unsigned long long)clock64() << 8) | (unsigned long long)(id); } } while (0)
+#define GLA_EVG(id) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && trace_n < 4096u) { \
+        P.trace[(threadIdx.x >> 5) * 4096u + trace_n++] = ((unsigned long long)globaltimer_ns() << 8) | (unsigned long long)(id); } } while (0)
 #else
 #define GLA_EV(id) do { } while (0)
+#define GLA_EVG(id) do { } while (0)
 #endif
 
 constexpr int kAggStride = kD * kD + kD;
@@ -743,6 +746,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         const int my_c = 16 * quad + (l & 15);          // state row (channel) of lanes 16-31
         const uint32_t rho = 16 * quad + (l & 15);      // output row of lanes 0-15
         float S[kD];
+        GLA_EV(62);
+        GLA_EVG(60);
         while (true) {
             const int item = next_item();
             if (item >= P.num_items) break;
@@ -961,6 +966,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             }
             __syncthreads();   // the item is drained
         }
+        GLA_EV(63);
+        GLA_EVG(61);
     } else if (w < kWarpGate) {
         // ==================================================================== score group
         // scores of the output-pass chunks: TMEM -> causal mask -> fp16 tile (takes the place of the raw gate tile
