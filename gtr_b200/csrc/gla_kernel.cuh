@@ -22,12 +22,19 @@
 // Tensor memory.  An M = 64 accumulator occupies lanes 0-15 of each 32-lane quadrant, so two
 // accumulators share the same columns at lane offsets 0 and 16.  A is produced as two N = 32
 // halves (key rows 0-31 at lane offset 0, 32-63 at offset 16); O sits at offset 0 and the
-// state increment at offset 16 of the same columns.  Every lane of the four compute warps
-// therefore owns useful data: lanes 0-15 of warp w hold row 16w+l of O (and the left half of
-// A), lanes 16-31 hold state row 16w+l-16 (and the right half of A).
+// state increment at offset 16 of the same columns.  Every lane of a warp that reads a quadrant
+// therefore owns useful data: lanes 0-15 of the warp on quadrant w hold row 16w+l of O (or the left
+// half of A), lanes 16-31 hold state row 16w+l-16 (or the right half of A).  Both the score
+// accumulator and the output/state accumulator are double-buffered.
 //
-// Warp roles: warps 0-7 gate group (operand preparation), warps 8-15 epilogue group (TMEM read-out,
-// state; warps e and e+4 share TMEM quadrant e and split its columns), warp 16 TMA producer, warp 17 MMA issue.
+// Shared memory.  A ring of kNumStages stages of {q, k, g, v} tiles filled by TMA (q and k are
+// rewritten in place as qh and kh, the gate tile is reused for the fp16 score tile), two tf32
+// operand buffers {qb, kb}, the fp16 copy of the running state, two output tiles and a block of
+// barriers and exchange rows.  A stage is handed back to the producer by the completion of the
+// chunk's last MMAs (tcgen05.commit on the stage's `empty` barrier), so its lifetime -- which,
+// divided by the ring depth, bounds the chunk rate -- does not include the epilogues.
+//
+// Warp roles: see the comment above gla_fwd_kernel.
 #pragma once
 
 #include "gla_device.cuh"
@@ -881,6 +888,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     const float b4 = ld_shared_f(smem_u32(&M.b4s[ctr % kSlots][my_c]));
                     const float dec = owner ? ex2(b4) : 0.f;
                     if (owner) gsum += b4;
+                    if (!GLA_DBGP(3))
 #pragma unroll
                     for (int hb = 0; hb < 2; ++hb) {        // two halves of 32 columns keep the register need bounded
                         float x[32];
@@ -936,7 +944,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         // lanes 0-15: output row into an output tile (the store warp sends it out)
                         const uint32_t j = c2 & 1u;
                         mbar_wait(ctx, &M.o_free[j], ((c2 >> 1) & 1u) ^ 1u);   // tile's previous store has read it
-                        store_row_f16<kD / 8>(owner ? base + kOffS16 : base + kOffOut + j * kTileBytes, rho, 0, S);
+                        if (!GLA_DBGP(3))
+                            store_row_f16<kD / 8>(owner ? base + kOffS16 : base + kOffOut + j * kTileBytes, rho, 0, S);
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (l == 0) {
@@ -992,7 +1001,9 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     group_wait(ctx, &M.a_done[b], (c2 >> 1) & 1u, quad, 3, kScoreThreads);
                     GLA_EV(10);
                     tc_fence_after();
-                    if (!M.wide[ctr % kSlots]) {
+                    if (GLA_DBGP(2)) {
+                        warp_arrive(&M.a_free[b], l);
+                    } else if (!M.wide[ctr % kSlots]) {
                         float x[32];
                         tmem_row<32>(tmem, quad, kTmA + 32u * b, x);
                         tc_fence_before();
