@@ -808,19 +808,27 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         const uint64_t t0 = globaltimer_ns();
                         while (true) {
                             const size_t sj = static_cast<size_t>(it.seq) * P.NS + j;
-                            uint32_t f = ld_acquire_gpu(P.flags + sj);
-                            while (f == 0u) {
-                                if (M.abort || ld_acquire_gpu(P.ctrl + 1) != 0u) break;
-                                if (globaltimer_ns() - t0 > ctx.deadline_span_ns) {
-                                    raise_timeout(ctx, WHERE_LOOKBACK);
-                                    break;
-                                }
-                                __nanosleep(64);
+                            // one lane per warp polls (the CTAs of later segments wait here for a whole pre-pass of
+                            // their predecessors: 128 polling threads each would only load the L2), the warp barrier of
+                            // the shuffle passes the acquired view on to the other lanes
+                            uint32_t f = 0u;
+                            if (l == 0) {
                                 f = ld_acquire_gpu(P.flags + sj);
+                                for (uint32_t n = 1; f == 0u; ++n) {
+                                    if ((n & 15u) == 0u) {
+                                        if (M.abort || ld_acquire_gpu(P.ctrl + 1) != 0u) break;
+                                        if (globaltimer_ns() - t0 > ctx.deadline_span_ns) {
+                                            raise_timeout(ctx, WHERE_LOOKBACK);
+                                            break;
+                                        }
+                                    }
+                                    __nanosleep(128);
+                                    f = ld_acquire_gpu(P.flags + sj);
+                                }
                             }
-                            // one decision per warp: the inclusive state only if every lane has seen it published
-                            const bool gave_up = __any_sync(0xffffffffu, f == 0u);
-                            const bool inclusive = __all_sync(0xffffffffu, f == 2u);
+                            f = __shfl_sync(0xffffffffu, f, 0);
+                            const bool gave_up = f == 0u;
+                            const bool inclusive = f == 2u;
                             if (gave_up) break;   // result undefined, status word set
                             const float dacc = ex2(dlog);
                             const float* src_row = inclusive ? P.incl + sj * (kD * kD) + my_c * kD
