@@ -13,6 +13,7 @@ region.  With N > 1 (torchrun, one rank per GPU) every rank runs the same per-GP
 on its own batch (weak scaling, no collective on the data path); the time is the max over
 ranks.  `--impl reference` times the reference's CPU path for this operator (its pure-PyTorch
 token recurrence, restated in oracle/gla_ref.py) on the host cores, on the same workload.
+`cpu_baseline` (the same recurrence, timed beside the GPU run) is reported by single-GPU runs only.
 """
 from __future__ import annotations
 
@@ -329,7 +330,9 @@ def run_ours(args, rank, local_rank, world):
         torch.cuda.synchronize()
         m = gla_ref.error_metrics(ref, o[:1].float().cpu())
         parity = {"rel_l2": m["rel_l2"], "max_abs": m["max_abs"], "finite": m["finite"]}
-        cpu_val, cpu_med, cpu_runs, cpu_threads, (cb, ct) = cpu_port_tokens_per_s(w["cfg"], max_tokens=1600)
+        # the CPU baseline is a single-GPU-run figure: under a multi-rank launch the host cores are shared with the
+        # other ranks' processes and the number means nothing
+        cpu = cpu_port_tokens_per_s(w["cfg"], max_tokens=1600) if world == 1 else None
         peak, peak_kind = measured_peak()
         tokens_per_step = B * T
         value = world * tokens_per_step * args.steps / (total_ms * 1e-3)
@@ -343,9 +346,10 @@ def run_ours(args, rank, local_rank, world):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo_bytes,
                          "kernel_us": kern_ms * 1e3, "traffic": ncu_traffic_bytes(args.workload)},
-            "cpu_baseline": {"value": cpu_val, "unit": "tokens/s", "cores": cpu_threads, "kind": "port",
-                             "sample": f"first {ct} of {T} tokens of every sequence (B{cb} H{H}), fp32 PyTorch token "
-                                       f"recurrence, median of {cpu_runs} runs ({cpu_med:.2f} s each)"},
+            "cpu_baseline": None if cpu is None else {
+                "value": cpu[0], "unit": "tokens/s", "cores": cpu[3], "kind": "port",
+                "sample": f"first {cpu[4][1]} of {T} tokens of every sequence (B{cpu[4][0]} H{H}), fp32 PyTorch token "
+                          f"recurrence, median of {cpu[2]} runs ({cpu[1]:.2f} s each)"},
             "e2e": {"value": world * tokens_per_step * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes, "steps": e2e_steps},
             "gpu_launches": args.steps, "clocks": clocks, "parity_check": parity, "backbone": backbone,
