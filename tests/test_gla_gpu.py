@@ -307,6 +307,55 @@ def test_fused_rmsnorm_swish_gate_epilogue(G, direction, grid, T):
     assert m2["finite"] and m2["rel_l2"] <= 2 * REL_L2, m2
 
 
+@pytest.mark.parametrize("scale", [1.0, 0.037, 3.5, -0.25, 0.0])
+def test_output_scales(G, scale):
+    """Positive scales ride in q's exponent inside the kernel, zero and negative ones are multiplied in at the
+    end: both must equal scale * (unscaled recurrence).  The final state never carries the scale."""
+    from oracle import c_oracle, gla_ref
+    q, k, v, g = gla_ref.make_inputs(2, 333, 3, seed=77)
+    ref, st_ref = c_oracle.forward(q, k, v, g, scale=scale, output_final_state=True)
+    got, st = _run(G, q, k, v, g, scale=scale, final=True, segments=2)
+    if scale == 0.0:
+        assert torch.isfinite(got).all() and float(got.abs().max()) == 0.0
+    else:
+        _check(ref, got)
+    assert ((st - st_ref).norm() / st_ref.norm()).item() < 5e-4   # increments come from fp16 operands
+
+
+@pytest.mark.parametrize("scale", [0.125, -0.5])
+def test_fused_epilogue_with_scales(G, scale):
+    from oracle import c_oracle, gla_ref
+    B, T, H = 1, 200, 2
+    q, k, v, g = gla_ref.make_inputs(B, T, H, seed=31)
+    gen = torch.Generator().manual_seed(6)
+    gate = torch.randn(B, T, H, 64, generator=gen).half()
+    w = (torch.randn(64, generator=gen).abs() + 0.5).half()
+    o_ref, _ = c_oracle.forward(q, k, v, g, scale=scale)
+    y_ref = gla_ref.rmsnorm_swish_gate(o_ref, gate, w, 1e-5)
+    ws = G.make_workspace(B, T, H, "cuda")
+    y = torch.full((B, T, H, 64), float("nan"), dtype=torch.float16, device="cuda")
+    G.chunk_gla_run_gated(q.cuda(), k.cuda(), v.cuda(), g.cuda(), gate.cuda(), w.cuda(), scale, 1e-5, ws, y)
+    G.check_status(ws)
+    m = gla_ref.error_metrics(y_ref, y.float().cpu())
+    assert m["finite"] and m["rel_l2"] <= REL_L2, m
+
+
+@pytest.mark.parametrize("direction", [0, 1])
+def test_strong_gates_across_segments(G, direction):
+    """Chunks on the exact-score path (decay beyond the tf32 path's range) mixed with ordinary ones, with the
+    sequence cut into segments so that both passes and the look-back see them."""
+    from oracle import c_oracle, gla_ref
+    B, T, H = 1, 640, 2
+    q, k, v, g = gla_ref.make_inputs(B, T, H, seed=41)
+    g = g.clone()
+    g[:, 100:260] = -2.0          # 64 tokens x -2 = e^-128 per chunk: exact path
+    g[:, 400:410, :, :8] = -30.0  # a burst in a few channels
+    ref, st_ref = c_oracle.forward(q, k, v, g, direction=direction, output_final_state=True)
+    got, st = _run(G, q, k, v, g, direction=direction, segments=3, final=True)
+    _check(ref, got)
+    assert ((st - st_ref).norm() / st_ref.norm()).item() < 5e-4
+
+
 def test_bounded_waits_time_out_cleanly(G):
     """A wait that nothing satisfies gives up after its limit, sets the status word, and the context
     stays usable (no trap, no hang): the operator runs correctly right afterwards."""
