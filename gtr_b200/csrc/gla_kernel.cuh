@@ -297,9 +297,10 @@ __device__ __noinline__ void logits_to_log_gates(uint8_t* tg, float inv_norm, in
 // scans.  Tiles are rows of 128 bytes whose 16-byte units are XOR-swizzled with (row & 7); a thread's first row
 // is a multiple of 8, so the swizzle of its i-th row depends on i only, a compile-time constant here.
 //
-// The hot variants (full chunk, tf32 path) are straight-line code without branches between rows, so
-// that the independent rows can be interleaved by the instruction scheduler; ragged chunks
-// and chunks on the exact path take out-of-line rolled versions.
+// The row loops are rolled (two to four rows per iteration, the running gate sum carried in registers and the
+// gate tile read a second time after the exchange): fully unrolled, the gate math alone was 50 KB of straight-line
+// code that every warp streamed through the instruction caches once per chunk, and instruction fetch was the
+// second largest stall of the kernel.  Ragged chunks and chunks on the exact path take out-of-line versions.
 struct GateLane {
     uint32_t a16;    // byte offset of (first logical row, first channel) in an fp16 tile, without the swizzle term
     uint32_t a32;    // same for the two-half tf32 tiles
@@ -333,6 +334,14 @@ __device__ __forceinline__ void unpack4(uint2 r, float* x) {
 }
 
 struct Gate4 { float v[4]; };
+#define GLA_PRAGMA_(x) _Pragma(#x)
+#define GLA_PRAGMA_UNROLL(n) GLA_PRAGMA_(unroll n)
+#ifndef GLA_GATE_UNROLL_A
+#define GLA_GATE_UNROLL_A 4
+#endif
+#ifndef GLA_GATE_UNROLL_B
+#define GLA_GATE_UNROLL_B 2
+#endif
 
 // Rolled, out-of-line row pass for the rare cases: a ragged last chunk (rows past `valid` are zeroed)
 // and chunks on the exact-score path (`wide`: G and raw q, k are stashed in plain layouts where the
@@ -403,36 +412,15 @@ __device__ __forceinline__ bool gate_math_t(const Ctx& c, uint32_t stage, uint32
         logits_to_log_gates(c.base + (tg - c.smem), P.inv_norm, 32 * w + l);
         named_bar_sync(bar_id, kTeamThreads);
     }
-    uint2 graw[R];
-#pragma unroll
-    for (int i = 0; i < R; ++i) graw[i] = ld_shared_v2(tg + off16<kRev>(gl, i));
-    GLA_EVC(c, 44);
-    float cs[R][4];
     {
         float a[4] = {0.f, 0.f, 0.f, 0.f};
-        if (!ragged) {
+        GLA_PRAGMA_UNROLL(GLA_GATE_UNROLL_A)
+        for (int i = 0; i < R; ++i) {
+            float gv[4];
+            unpack4(ld_shared_v2(tg + off16<kRev>(gl, i)), gv);
+            const bool live = 16 * w + 8 * (l >> 4) + i < valid;
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                float gv[4];
-                unpack4(graw[i], gv);
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    a[ch] = fmaf(gv[ch], kLog2e, a[ch]);
-                    cs[i][ch] = a[ch];
-                }
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < R; ++i) {
-                float gv[4];
-                unpack4(graw[i], gv);
-                const bool live = 16 * w + 8 * (l >> 4) + i < valid;
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    a[ch] += live ? gv[ch] * kLog2e : 0.f;
-                    cs[i][ch] = a[ch];
-                }
-            }
+            for (int ch = 0; ch < 4; ++ch) a[ch] = fmaf(live ? gv[ch] : 0.f, kLog2e, a[ch]);
         }
         st_shared_f4(tot_sa + grp * kD * 4, a[0], a[1], a[2], a[3]);
     }
@@ -474,32 +462,29 @@ __device__ __forceinline__ bool gate_math_t(const Ctx& c, uint32_t stage, uint32
     if (ragged || wide) {
         gate_rows_general<kRev>(c, stage, qbar, valid, w, l, kStateOnly, wide, off, b4, e1, e2);
     } else {
-        float ck[4], oq[4];
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-            ck[ch] = b4.v[ch] - off.v[ch];
-            oq[ch] = off.v[ch] + P.q_exp;
-        }
-#pragma unroll
+        float r[4] = {off.v[0], off.v[1], off.v[2], off.v[3]};   // running inclusive gate sum of the current row
+        const float qx = P.q_exp;
+        GLA_PRAGMA_UNROLL(GLA_GATE_UNROLL_B)
         for (int i = 0; i < R; ++i) {
-            float kv[4], kh[4];
-            unpack4(ld_shared_v2(tk + off16<kRev>(gl, i)), kv);   // k and q rows are read where they are used:
-                                                                  // held across the barrier they cost 32 registers
+            float gv[4], kv[4], kh[4];
+            unpack4(ld_shared_v2(tg + off16<kRev>(gl, i)), gv);
+            unpack4(ld_shared_v2(tk + off16<kRev>(gl, i)), kv);
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) kh[ch] = kv[ch] * ex2(ck[ch] - cs[i][ch]);
+            for (int ch = 0; ch < 4; ++ch) {
+                r[ch] = fmaf(gv[ch], kLog2e, r[ch]);
+                kh[ch] = kv[ch] * ex2(b4.v[ch] - r[ch]);
+            }
             st_shared_v2(tk + off16<kRev>(gl, i), pack_half2(kh[0], kh[1]), pack_half2(kh[2], kh[3]));
             if (!kStateOnly) {
                 float qv[4], qh[4];
                 unpack4(ld_shared_v2(tq + off16<kRev>(gl, i)), qv);
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) qh[ch] = qv[ch] * ex2(oq[ch] + cs[i][ch]);
+                for (int ch = 0; ch < 4; ++ch) qh[ch] = qv[ch] * ex2(r[ch] + qx);
                 st_shared_v2(tq + off16<kRev>(gl, i), pack_half2(qh[0], qh[1]), pack_half2(qh[2], qh[3]));
-                if (!GLA_DBG(1)) {
-                    st_shared_f4(qbar + off32<kRev>(gl, i), round_tf32(qh[0] * e1.v[0]), round_tf32(qh[1] * e1.v[1]),
-                                 round_tf32(qh[2] * e1.v[2]), round_tf32(qh[3] * e1.v[3]));
-                    st_shared_f4(kbar + off32<kRev>(gl, i), round_tf32(kh[0] * e2.v[0]), round_tf32(kh[1] * e2.v[1]),
-                                 round_tf32(kh[2] * e2.v[2]), round_tf32(kh[3] * e2.v[3]));
-                }
+                st_shared_f4(qbar + off32<kRev>(gl, i), round_tf32(qh[0] * e1.v[0]), round_tf32(qh[1] * e1.v[1]),
+                             round_tf32(qh[2] * e1.v[2]), round_tf32(qh[3] * e1.v[3]));
+                st_shared_f4(kbar + off32<kRev>(gl, i), round_tf32(kh[0] * e2.v[0]), round_tf32(kh[1] * e2.v[1]),
+                             round_tf32(kh[2] * e2.v[2]), round_tf32(kh[3] * e2.v[3]));
             }
         }
     }
