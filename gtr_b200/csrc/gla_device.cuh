@@ -33,9 +33,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// GLA_WAIT_MODE: 0 try_wait with a suspend-time hint, 1 try_wait without hint, 2 test_wait (never suspends)
+// One poll of an mbarrier phase.  GLA_WAIT_MODE: 1 try_wait (suspends the thread for a system-chosen time while the
+// phase is incomplete; default, measured fastest), 0 try_wait with an explicit suspend-time hint, 2 test_wait (never
+// suspends).
 #ifndef GLA_WAIT_MODE
-#define GLA_WAIT_MODE 0
+#define GLA_WAIT_MODE 1
 #endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
