@@ -90,9 +90,12 @@ WsLayout ws_layout(size_t nseq, size_t ns) {
     L.ctrl = 0;
     L.flags = 256;
     L.clear_bytes = 256 + align_up(nseq * ns * 4, 256);
+    // segment aggregates and inclusive states are exchanged between the work items of one sequence only:
+    // unsegmented sequences (ns == 1) need none, whatever their number
+    const size_t slots = ns > 1 ? nseq * ns : 0;
     L.agg = L.clear_bytes;
-    L.incl = L.agg + align_up(nseq * ns * gla::kAggStride * 4, 256);
-    L.total = L.incl + align_up(nseq * ns * gla::kD * gla::kD * 4, 256);
+    L.incl = L.agg + align_up(slots * gla::kAggStride * 4, 256);
+    L.total = L.incl + align_up(slots * gla::kD * gla::kD * 4, 256);
     return L;
 }
 

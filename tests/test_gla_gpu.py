@@ -356,6 +356,21 @@ def test_strong_gates_across_segments(G, direction):
     assert ((st - st_ref).norm() / st_ref.norm()).item() < 5e-4
 
 
+def test_unsegmented_sequences_need_only_the_control_words(G):
+    """One work item per sequence exchanges no states between items: 512 bytes of scratch are enough."""
+    from oracle import c_oracle, gla_ref
+    B, T, H = 2, 640, 3
+    q, k, v, g = gla_ref.make_inputs(B, T, H, seed=51)
+    ref, _ = c_oracle.forward(q, k, v, g)
+    ws = torch.zeros(128, dtype=torch.float32, device="cuda")
+    o = torch.full((B, T, H, 64), float("nan"), dtype=torch.float16, device="cuda")
+    G.chunk_gla_run(q.cuda(), k.cuda(), v.cuda(), g.cuda(), 0.125, ws, o, segments=T)
+    G.check_status(ws)
+    _check(ref, o.float().cpu())
+    with pytest.raises(Exception):      # three segments per sequence do not fit in it
+        G.chunk_gla_run(q.cuda(), k.cuda(), v.cuda(), g.cuda(), 0.125, ws, o, segments=4)
+
+
 def test_bounded_waits_time_out_cleanly(G):
     """A wait that nothing satisfies gives up after its limit, sets the status word, and the context
     stays usable (no trap, no hang): the operator runs correctly right afterwards."""
