@@ -51,9 +51,6 @@ constexpr int kStageBytes = 4 * kTileBytes;
 #ifndef GLA_STAGES
 #define GLA_STAGES 4
 #endif
-#ifndef GLA_L2_PREFETCH
-#define GLA_L2_PREFETCH 0         // chunks ahead of the shared-memory ring that the producer asks for in the L2
-#endif
 constexpr int kCtasPerSm = GLA_MIN_CTAS;    // resident CTAs per SM the launch bounds and the grid size assume
 constexpr int kNumStages = GLA_STAGES;
 // Five warpgroups of four warps: state group, score group, two gate teams, service warps.
@@ -1071,26 +1068,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                 for (int pass = 0; pass < npass; ++pass) {
                     const bool state_only = it.state_pass && pass == 0;
                     BoxWalker bw(P, it.first_chunk * kChunk);
-#if GLA_L2_PREFETCH > 0
-                    // the shared-memory ring is short, so the chunks further ahead are asked for in the L2
-                    BoxWalker bwp(P, (it.first_chunk + GLA_L2_PREFETCH) * kChunk);
-#endif
                     for (int i = 0; i < it.nchunks; ++i, ++ctr) {
                         const uint32_t s = ctr % kNumStages, n = ctr / kNumStages;
-#if GLA_L2_PREFETCH > 0
-                        if (i + GLA_L2_PREFETCH < it.nchunks) {
-                            if (elect_one()) {
-                                bwp.for_each(P, [&](int id, int r, int c, int) {
-                                    if (!state_only) tma_prefetch_l2_5d(&maps.m[TQ][id], 0, it.h, r, c, it.b);
-                                    tma_prefetch_l2_5d(&maps.m[TK][id], 0, it.h, r, c, it.b);
-                                    tma_prefetch_l2_5d(&maps.m[TG][id], 0, it.h, r, c, it.b);
-                                    tma_prefetch_l2_5d(&maps.m[TV][id], 0, it.h, r, c, it.b);
-                                });
-                            }
-                            __syncwarp();
-                            bwp.advance(P);
-                        }
-#endif
                         mbar_wait(ctx, &M.empty[s], (n & 1u) ^ 1u);
                         GLA_EV(30);
                         if (elect_one()) {
