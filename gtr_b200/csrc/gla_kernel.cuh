@@ -642,6 +642,7 @@ __device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
 // the score read-out is therefore a group of its own and overlaps it.  The gate group is throughput work and runs
 // up to two chunks ahead (bounded by the tf32 buffers).  Each warpgroup sets its own register budget (setmaxnreg):
 // the state group holds a 64-wide state row per thread, the four service warps need next to nothing.
+//
 // Register budgets per thread of the five warpgroups.  setmaxnreg only re-divides what the CTA got at launch
 // (kThreads x the kernel's register count, 96 under these launch bounds), and an increase waits, without limit, until
 // the other groups have released enough: the budgets must not add up to more than that.
