@@ -236,9 +236,23 @@ __device__ __forceinline__ float2 unpack_half2(uint32_t u) {
     __half2 h = *reinterpret_cast<__half2*>(&u);
     return __half22float2(h);
 }
+__device__ __forceinline__ float lg2(float x) {   // log2(x), one MUFU op
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// log(sigmoid(x)) = min(x, 0) - log(1 + exp(-|x|)), with the two MUFU ops ex2 and lg2; absolute error
+// below 1e-6, far inside the fp16 grid the result is rounded to
 __device__ __forceinline__ float logsigmoid_f(float x) {
-    // log(sigmoid(x)) = min(x, 0) - log1p(exp(-|x|))
-    return fminf(x, 0.f) - log1pf(__expf(-fabsf(x)));
+    const float t = ex2(-fabsf(x) * 1.4426950408889634f);
+    return fminf(x, 0.f) - 0.6931471805599453f * lg2(1.f + t);
+}
+// x * sigmoid(x) = h + h * tanh(h) with h = x / 2: one MUFU op (tanh.approx, relative error about 2^-11)
+__device__ __forceinline__ float silu_f(float x) {
+    const float h = 0.5f * x;
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+    return fmaf(h, t, h);
 }
 
 __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t a) {

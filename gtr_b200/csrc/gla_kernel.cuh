@@ -37,6 +37,8 @@
 // Warp roles: see the comment above gla_fwd_kernel.
 #pragma once
 
+#include <type_traits>
+
 #include "gla_device.cuh"
 
 namespace gla {
@@ -272,17 +274,6 @@ __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) { st_shared_u32(a,
 __device__ __forceinline__ void sts64(uint32_t a, float x, float y) { st_shared_f2(a, x, y); }
 
 // ------------------------------------------------------------------------------------------
-// Raw-logit gates (gk_normalizer > 0): rewrite the gate tile in place as fp16 log gates,
-// logsigmoid(x) / normalizer, before the gate math reads it.  Kept out of line and rolled: it is
-// a rarely used mode and must not bloat the main loop.
-__device__ __noinline__ void logits_to_log_gates(uint8_t* tg, float inv_norm, int tid) {
-    for (int e = tid; e < kChunk * kD / 2; e += kTeamThreads) {
-        uint32_t* p = reinterpret_cast<uint32_t*>(tg) + e;
-        const float2 x = unpack_half2(*p);
-        *p = pack_half2_sat(logsigmoid_f(x.x) * inv_norm, logsigmoid_f(x.y) * inv_norm);
-    }
-}
-
 #ifdef GLA_TRACE
 #define GLA_DBG(bit) ((c.p->dbg >> (bit)) & 1)
 #define GLA_DBGP(bit) ((P.dbg >> (bit)) & 1)
@@ -392,7 +383,7 @@ __device__ __noinline__ void gate_rows_general(const Ctx& c, uint32_t stage, uin
     }
 }
 
-template <bool kStateOnly, bool kRev>
+template <bool kStateOnly, bool kRev, bool kLogits>
 __device__ __forceinline__ bool gate_math_t(const Ctx& c, uint32_t stage, uint32_t qbar, int n, int valid, int w, int l,
                                             uint64_t* buf_bar, uint32_t buf_parity, uint32_t bar_id) {
     constexpr int R = 8;
@@ -408,16 +399,21 @@ __device__ __forceinline__ bool gate_math_t(const Ctx& c, uint32_t stage, uint32
     const bool ragged = valid < kChunk;
 
     GLA_EVC(c, 45);
-    if (P.inv_norm > 0.f) {
-        logits_to_log_gates(c.base + (tg - c.smem), P.inv_norm, 32 * w + l);
-        named_bar_sync(bar_id, kTeamThreads);
-    }
     {
         float a[4] = {0.f, 0.f, 0.f, 0.f};
+        const float inv_norm = P.inv_norm;
         GLA_PRAGMA_UNROLL(GLA_GATE_UNROLL_A)
         for (int i = 0; i < R; ++i) {
             float gv[4];
             unpack4(ld_shared_v2(tg + off16<kRev>(gl, i)), gv);
+            if constexpr (kLogits) {
+                // raw-logit gates (gk_normalizer > 0): the tile is rewritten in place as fp16 log gates,
+                // logsigmoid(x) / normalizer; each thread converts the rows it owns and reads only those later
+                const uint32_t h0 = pack_half2_sat(logsigmoid_f(gv[0]) * inv_norm, logsigmoid_f(gv[1]) * inv_norm);
+                const uint32_t h1 = pack_half2_sat(logsigmoid_f(gv[2]) * inv_norm, logsigmoid_f(gv[3]) * inv_norm);
+                st_shared_v2(tg + off16<kRev>(gl, i), h0, h1);
+                unpack4(make_uint2(h0, h1), gv);
+            }
             const bool live = 16 * w + 8 * (l >> 4) + i < valid;
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) a[ch] = fmaf(live ? gv[ch] : 0.f, kLog2e, a[ch]);
@@ -497,12 +493,17 @@ __device__ __forceinline__ bool gate_math_t(const Ctx& c, uint32_t stage, uint32
 // Returns whether the chunk took the exact-score path (always false for state-only chunks).
 __device__ __forceinline__ bool gate_math(const Ctx& c, uint32_t stage, uint32_t qbar, int n, int valid, int w, int l,
                                           bool state_only, uint64_t* buf_bar, uint32_t buf_parity, uint32_t bar_id) {
+    // one instantiation per (pass, scan direction, gate kind): a launch runs two of them, and the others cost it
+    // neither registers nor instruction-cache space
+    const bool logits = c.p->inv_norm > 0.f;
+#define GLA_GATE_CALL(SO, RV, LG) gate_math_t<SO, RV, LG>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity, bar_id)
     if (c.p->rev) {
-        if (state_only) return gate_math_t<true, true>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity, bar_id);
-        return gate_math_t<false, true>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity, bar_id);
+        if (state_only) return logits ? GLA_GATE_CALL(true, true, true) : GLA_GATE_CALL(true, true, false);
+        return logits ? GLA_GATE_CALL(false, true, true) : GLA_GATE_CALL(false, true, false);
     }
-    if (state_only) return gate_math_t<true, false>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity, bar_id);
-    return gate_math_t<false, false>(c, stage, qbar, n, valid, w, l, buf_bar, buf_parity, bar_id);
+    if (state_only) return logits ? GLA_GATE_CALL(true, false, true) : GLA_GATE_CALL(true, false, false);
+    return logits ? GLA_GATE_CALL(false, false, true) : GLA_GATE_CALL(false, false, false);
+#undef GLA_GATE_CALL
 }
 
 __device__ __forceinline__ uint32_t sw_f16(uint32_t row, uint32_t col) {     // col in fp16 elements
@@ -871,10 +872,39 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         if (rr < 0) { rr += P.Hc; --cc; }
                     }
                 }
+                // two instantiations of the chunk loop: the fused epilogue keeps 32 more registers alive per thread and
+                // must not weigh on the plain operator
+                auto run_chunks = [&](auto gated_tag) {
+                constexpr bool kGated = decltype(gated_tag)::value;
                 for (int i = 0; i < it.nchunks; ++i, ++ctr) {
                     // lanes 0-15: output row -> fp16 output tile
                     // lanes 16-31: S <- 2^(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
                     const uint32_t p = ctr & 1u;
+                    // fused epilogue: the output gate of this thread's row is asked for before the wait, so that the
+                    // global-memory latency is not spent on the chain from one chunk's state to the next
+                    uint4 gt[kGated ? kD / 8 : 1];
+                    bool live = false;
+                    if constexpr (kGated) {
+                        live = !owner && u >= 0 && u < P.T;
+                        if (live) {
+                            // the token read at this row of the chunk follows the same mapping as the TMA boxes
+                            const long long tok = (P.Wc > 1) ? static_cast<long long>(rr) * P.Wc + cc : u;
+                            const uint4* gp = reinterpret_cast<const uint4*>(
+                                P.gate + it.b * P.gate_sb + tok * P.gate_st + it.h * P.gate_sh);
+#pragma unroll
+                            for (int m = 0; m < kD / 8; ++m) gt[m] = __ldg(gp + m);
+                        }
+                        // next chunk: 64 steps further along the scan
+                        if (!P.rev) {
+                            u += kChunk;
+                            rr += kChunk;
+                            while (rr >= P.Hc) { rr -= P.Hc; ++cc; }
+                        } else {
+                            u -= kChunk;
+                            rr -= kChunk;
+                            while (rr < 0) { rr += P.Hc; --cc; }
+                        }
+                    }
                     group_wait(ctx, &M.os_done[p], (ctr >> 1) & 1u, w, 2, kStateThreads);
                     GLA_EV(14);
                     tc_fence_after();
@@ -895,62 +925,61 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     tc_fence_before();
                     warp_arrive(&M.os_free[p], l);
                     if (!state_only) {
-                        if (P.gated) {
-                            // y = o * rsqrt(mean(o^2) + eps) * w * silu(gate) on the output rows (lanes 0-15);
-                            // the token read at this row of the chunk follows the same mapping as the TMA boxes
-                            if (!owner && u >= 0 && u < P.T) {
+                        const uint32_t j = c2 & 1u;
+                        if constexpr (kGated) {
+                            // the fp16 copy of the new state goes out first: the next chunk's read-out waits for it
+                            if (owner && !GLA_DBGP(3)) store_row_f16<kD / 8>(base + kOffS16, rho, 0, S);
+                            fence_proxy_async_smem();
+                            if (i + 1 < it.nchunks) warp_arrive(&M.s16_ready, l);
+                            // y = o * rsqrt(mean(o^2) + eps) * w * silu(gate) on the output rows (lanes 0-15)
+                            if (live) {
                                 float ss = 0.f;
 #pragma unroll
                                 for (int v = 0; v < kD; ++v) ss = fmaf(S[v], S[v], ss);
                                 const float rinv = P.o_mul * rsqrtf(ss * (P.o_mul * P.o_mul) * (1.f / kD) + P.rms_eps);
-                                const long long tok = (P.Wc > 1) ? static_cast<long long>(rr) * P.Wc + cc : u;
-                                const uint4* gp = reinterpret_cast<const uint4*>(
-                                    P.gate + it.b * P.gate_sb + tok * P.gate_st + it.h * P.gate_sh);
                                 const uint4* wp = reinterpret_cast<const uint4*>(P.rms_w);
 #pragma unroll
                                 for (int m = 0; m < kD / 8; ++m) {
-                                    const uint4 g4 = __ldg(gp + m), w4 = __ldg(wp + m);
+                                    const uint4 g4 = gt[m], w4 = __ldg(wp + m);
                                     const uint32_t gu[4] = {g4.x, g4.y, g4.z, g4.w}, wu[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
                                     for (int q2 = 0; q2 < 4; ++q2) {
                                         const float2 gf = unpack_half2(gu[q2]), wf = unpack_half2(wu[q2]);
-                                        S[8 * m + 2 * q2] *= rinv * wf.x * (gf.x / (1.f + __expf(-gf.x)));
-                                        S[8 * m + 2 * q2 + 1] *= rinv * wf.y * (gf.y / (1.f + __expf(-gf.y)));
+                                        S[8 * m + 2 * q2] *= rinv * wf.x * silu_f(gf.x);
+                                        S[8 * m + 2 * q2 + 1] *= rinv * wf.y * silu_f(gf.y);
                                     }
                                 }
                             }
-                            // next chunk: 64 steps further along the scan
-                            if (!P.rev) {
-                                u += kChunk;
-                                rr += kChunk;
-                                while (rr >= P.Hc) { rr -= P.Hc; ++cc; }
-                            } else {
-                                u -= kChunk;
-                                rr -= kChunk;
-                                while (rr < 0) { rr += P.Hc; --cc; }
-                            }
-                        } else if (P.o_mul != 1.f) {      // scale not folded into q (zero, negative or not finite)
-                            const float mul = owner ? 1.f : P.o_mul;
+                            mbar_wait(ctx, &M.o_free[j], ((c2 >> 1) & 1u) ^ 1u);   // tile's previous store has read it
+                            if (!owner && !GLA_DBGP(3)) store_row_f16<kD / 8>(base + kOffOut + j * kTileBytes, rho, 0, S);
+                            fence_proxy_async_smem();
+                            warp_arrive(&M.o_ready[j], l);
+                        } else {
+                            if (P.o_mul != 1.f) {         // scale not folded into q (zero, negative or not finite)
+                                const float mul = owner ? 1.f : P.o_mul;
 #pragma unroll
-                            for (int v = 0; v < kD; ++v) S[v] *= mul;
-                        }
-                        // lanes 16-31: fp16 copy of the new state for the next chunk's read-out;
-                        // lanes 0-15: output row into an output tile (the store warp sends it out)
-                        const uint32_t j = c2 & 1u;
-                        mbar_wait(ctx, &M.o_free[j], ((c2 >> 1) & 1u) ^ 1u);   // tile's previous store has read it
-                        if (!GLA_DBGP(3))
-                            store_row_f16<kD / 8>(owner ? base + kOffS16 : base + kOffOut + j * kTileBytes, rho, 0, S);
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (l == 0) {
-                            if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.s16_ready));
-                            mbar_arrive(smem_u32(&M.o_ready[j]));
+                                for (int v = 0; v < kD; ++v) S[v] *= mul;
+                            }
+                            // lanes 16-31: fp16 copy of the new state for the next chunk's read-out;
+                            // lanes 0-15: output row into an output tile (the store warp sends it out)
+                            mbar_wait(ctx, &M.o_free[j], ((c2 >> 1) & 1u) ^ 1u);   // tile's previous store has read it
+                            if (!GLA_DBGP(3))
+                                store_row_f16<kD / 8>(owner ? base + kOffS16 : base + kOffOut + j * kTileBytes, rho, 0, S);
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (l == 0) {
+                                if (i + 1 < it.nchunks) mbar_arrive(smem_u32(&M.s16_ready));
+                                mbar_arrive(smem_u32(&M.o_ready[j]));
+                            }
                         }
                         ++c2;
                         GLA_EV(15);
                     }
                     GLA_EV(16);
                 }
+                };
+                if (!state_only && P.gated) run_chunks(std::true_type{});
+                else run_chunks(std::false_type{});
 
                 if (state_only) {
                     if (it.seg == 0) {
