@@ -5,7 +5,8 @@ Mirrors, for inference only, the reference's
 * ``GatedLinearAttention`` after ``convert_to_deploy`` (engine/gtr/backbone/vit_adapter.py:338-418
   fused q/k/v/g/gk_low projection, :435-605 forward): one fused GEMM, the low-rank gate head,
   the GLA operator with the RMSNorm * w * silu(g) epilogue, ``o_proj``;
-* ``SpatialSwiGLU`` in its split-GEMM deploy form (engine/gtr/backbone/vit_adapter_spatial_swiglu.py:21-70);
+* ``SpatialSwiGLU`` in its split-GEMM deploy form (engine/gtr/backbone/vit_adapter_spatial_swiglu.py:21-70), with the
+  depthwise convolution, bias, silu(gate) and the product fused into one kernel (``ops.swiglu_dwconv``);
 * ``Block`` (vit_adapter.py:608-642) and the CLS-free ``VisionTransformerSpatialSwiGLU`` forward
   (vit_adapter_spatial_swiglu.py:96-127) on top of the conv-pyramid patch-16 stem
   (vit_adapter.py:188-204).
@@ -115,15 +116,22 @@ class SpatialSwiGLU(nn.Module):
             if bias is not None:
                 self.dwconv.bias.copy_(bias)
 
+    def _taps(self) -> torch.Tensor:
+        """The depthwise weight as [3, 3, C] (tap-major), rebuilt when the parameter changes."""
+        w = self.dwconv.weight
+        key = (w.data_ptr(), w._version, w.device, w.dtype)
+        if getattr(self, "_taps_key", None) != key:
+            self._taps_cache = w.detach()[:, 0].permute(1, 2, 0).contiguous()
+            self._taps_key = key
+        return self._taps_cache
+
     def forward(self, x: torch.Tensor, grid_hw: Tuple[int, int]) -> torch.Tensor:
-        B, L, _ = x.shape
-        hg, wg = grid_hw
         gate = F.linear(x, self.gate_w)
         y = F.linear(x, self.value_w)                              # [B, L, C]
-        y = y.view(B, hg, wg, -1).permute(0, 3, 1, 2)              # channels-last view of [B, C, hg, wg]
-        y = self.dwconv(y)
-        y = y.permute(0, 2, 3, 1).reshape(B, L, -1)
-        return self.down_proj(F.silu(gate) * y)
+        # depthwise 3x3 conv on the patch grid, bias, silu(gate) and the product in one pass over memory, on
+        # tokens in place (the reference views y as a channels-last image for cuDNN and back)
+        z = ops.swiglu_dwconv(gate, y, self._taps(), self.dwconv.bias, grid_hw)
+        return self.down_proj(z)
 
 
 class Block(nn.Module):

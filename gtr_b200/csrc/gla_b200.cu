@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "gla_kernel.cuh"
+#include "swiglu_dwconv.cuh"
 
 namespace {
 
@@ -437,6 +438,26 @@ int gla_b200_rmsnorm_gated(const void* x, const void* g, const void* w, void* y,
         static_cast<__half*>(y), rows, eps);
     cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) { note_cuda("rmsnorm launch", e); return GLA_B200_ERR_CUDA; }
+    return GLA_B200_OK;
+}
+
+int gla_b200_swiglu_dwconv(const void* gate, const void* y, const void* weight, const void* bias, void* out,
+                           int32_t B, int32_t grid_h, int32_t grid_w, int32_t C, void* stream) {
+    if (B < 0 || grid_h < 0 || grid_w < 0 || C <= 0 || (C & 7)) return GLA_B200_ERR_SHAPE;
+    if (static_cast<int64_t>(B) * grid_h * grid_w == 0) return GLA_B200_OK;
+    if (!gate || !y || !weight || !out) return GLA_B200_ERR_NULL;
+    if (!aligned16(gate) || !aligned16(y) || !aligned16(weight) || !aligned16(out) || (bias && !aligned16(bias)))
+        return GLA_B200_ERR_ALIGN;
+    if (out == gate || out == y) return GLA_B200_ERR_ARG;      // neighbours are read after their own output is written
+    const int64_t strips = (grid_w + gla::kDwStrip - 1) / gla::kDwStrip;
+    const int64_t threads = static_cast<int64_t>(B) * grid_h * strips * (C >> 3);
+    const int64_t blocks = (threads + 127) / 128;
+    if (blocks > 0x7fffffffLL) return GLA_B200_ERR_SHAPE;
+    gla::swiglu_dwconv_kernel<<<static_cast<unsigned>(blocks), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(gate), static_cast<const __half*>(y), static_cast<const __half*>(weight),
+        static_cast<const __half*>(bias), static_cast<__half*>(out), B, grid_h, grid_w, C);
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) { note_cuda("swiglu_dwconv launch", e); return GLA_B200_ERR_CUDA; }
     return GLA_B200_OK;
 }
 

@@ -182,3 +182,36 @@ def rmsnorm_gated(x, g, w, y, eps: float) -> None:
         stream = torch.cuda.current_stream(x.device).cuda_stream
         _lib.check(_lib.lib().gla_b200_rmsnorm_gated(x.data_ptr(), g.data_ptr(), w.data_ptr(), y.data_ptr(),
                                                      rows, kV, float(eps), ctypes.c_void_p(stream)))
+
+
+def swiglu_dwconv(gate: torch.Tensor, y: torch.Tensor, weight_taps: torch.Tensor, bias: Optional[torch.Tensor],
+                  grid_hw: Tuple[int, int], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = silu(gate) * (bias + depthwise 3x3 conv of y on the patch grid), tokens in [B, L, C] layout.
+
+    The middle of the reference's SpatialSwiGLU in deploy form (vit_adapter_spatial_swiglu.py:50-60) as one kernel.
+    ``weight_taps`` is the depthwise weight as fp16 [3, 3, C] (``conv.weight[:, 0].permute(1, 2, 0)``), already
+    oriented for the canonical grid."""
+    hg, wg = int(grid_hw[0]), int(grid_hw[1])
+    for t, name in ((gate, "gate"), (y, "y")):
+        if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 3 or not t.is_contiguous():
+            raise RuntimeError(f"{name} must be a contiguous float16 CUDA tensor [B, L, C]")
+    B, L, C = y.shape
+    if gate.shape != y.shape or L != hg * wg or C % 8:
+        raise RuntimeError(f"gate/y shapes {tuple(gate.shape)}/{tuple(y.shape)} do not fit a {hg}x{wg} grid "
+                           "(C must be a multiple of 8)")
+    if weight_taps.dtype != torch.float16 or tuple(weight_taps.shape) != (3, 3, C) or not weight_taps.is_contiguous() \
+            or weight_taps.device != y.device:
+        raise RuntimeError("weight_taps must be a contiguous float16 [3, 3, C] tensor on y's device")
+    if bias is not None and (bias.dtype != torch.float16 or bias.numel() != C or not bias.is_contiguous()
+                             or bias.device != y.device):
+        raise RuntimeError("bias must be a contiguous float16 vector of C elements on y's device")
+    if out is None:
+        out = torch.empty_like(y)
+    elif out.shape != y.shape or out.dtype != torch.float16 or not out.is_contiguous() or out.device != y.device:
+        raise RuntimeError("out must match y")
+    with torch.cuda.device(y.device):
+        stream = torch.cuda.current_stream(y.device).cuda_stream
+        _lib.check(_lib.lib().gla_b200_swiglu_dwconv(gate.data_ptr(), y.data_ptr(), weight_taps.data_ptr(),
+                                                     bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                                     B, hg, wg, C, ctypes.c_void_p(stream)))
+    return out

@@ -121,6 +121,15 @@ int gla_b200_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint
 int gla_b200_rmsnorm_gated(const void* x, const void* g, const void* w, void* y,
                            int64_t rows, int32_t D, float eps, void* stream);
 
+/* Middle step of the backbone's Spatial SwiGLU MLP in its deploy form
+ * (engine/gtr/backbone/vit_adapter_spatial_swiglu.py:50-60: view as grid -> 3x3 depthwise conv -> view back ->
+ * silu(gate) * y), in one pass:  out = silu(gate) * (bias + dwconv3x3(y))  on tokens laid out [B, grid_h*grid_w, C],
+ * zero padding at the grid border.  gate, y, out: fp16 [B, grid_h*grid_w, C] contiguous, out distinct from both;
+ * weight: fp16 [3][3][C] (tap-major: the reference's [C,1,3,3] weight permuted, already oriented for the
+ * canonical grid); bias: fp16 [C] or NULL.  C a multiple of 8. */
+int gla_b200_swiglu_dwconv(const void* gate, const void* y, const void* weight, const void* bias, void* out,
+                           int32_t B, int32_t grid_h, int32_t grid_w, int32_t C, void* stream);
+
 /* Shape of GLAPlugin::enqueue (tensorrt_plugin/trt_plugin/gla_plugin.cu:124-163): `inputs` holds
  * q,k,v,gk[,g,rms_w] device pointers, `outputs[0]` the result, dims are those of q [B,T,H,K];
  * the fused epilogue is used iff n_inputs == 6 and rms_eps > 0 (gla_plugin.cu:150).
