@@ -161,7 +161,9 @@ class ConvPyramidPatchEmbed(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         for conv in self.convs:
             x = F.relu(conv(x))
-        return self.proj(x).flatten(2).transpose(1, 2)
+        # tokens as a dense [B, L, C] tensor: a transposed view here would hand its strides on to every
+        # residual sum of the backbone (strided adds, a copy in front of each LayerNorm)
+        return self.proj(x).flatten(2).transpose(1, 2).contiguous()
 
 
 class GTRBackbone(nn.Module):
