@@ -190,7 +190,7 @@ def run_backbone(args, rank, local_rank, world, dist):
         return {"unavailable": f"batch {total_batch} does not divide over {world} ranks"}
     b = total_batch // world
     torch.manual_seed(0)
-    model = GTRBackbone().half().to(dev).eval()
+    model = GTRBackbone().half().to(dev).eval().convert_to_deploy()
     runner = GraphedBackbone(model)
     img = torch.rand(b, 3, 1024, 2048, generator=torch.Generator().manual_seed(rank)).half().to(dev)
     steps = args.backbone_steps

@@ -66,6 +66,7 @@ class GatedLinearAttention(nn.Module):
         self.scale = HEAD_DIM ** -0.5
         self._ws_key = None
         self._ws = self._out = None
+        self._folded = False
 
     def _gla_buffers(self, B: int, T: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
         """Workspace and output are kept per shape so that captured graphs see stable pointers
@@ -77,14 +78,33 @@ class GatedLinearAttention(nn.Module):
             self._ws_key = key
         return self._ws, self._out
 
+    @torch.no_grad()
+    def fold_gate_head(self) -> None:
+        """Deploy-time weight folding: gk = (x W_low^T) W_high^T + b = x (W_high W_low)^T + b becomes key_dim more
+        columns of the fused projection, with the bias in that GEMM's epilogue.  The low-rank form saves FLOPs that
+        a B200 does not miss; it costs a K = 16 GEMM that is bound by writing its output, a separate bias kernel and
+        a strided read of the 16 low-rank columns per block."""
+        if self._folded:
+            return
+        W = self.qkv_g_gkl_proj.weight
+        main = sum(self.split[:4])
+        w_gk = (self.gk_high_proj.weight.float() @ W[main:].float()).to(W.dtype)
+        self.fused_w = nn.Parameter(torch.cat([W[:main], w_gk], dim=0).contiguous(), requires_grad=False)
+        self.fused_b = nn.Parameter(torch.cat([torch.zeros(main, dtype=W.dtype, device=W.device),
+                                               self.gk_high_proj.bias.to(W.dtype)]).contiguous(), requires_grad=False)
+        self._folded = True
+
     def forward(self, x: torch.Tensor, direction: int = 0, grid_hw: Optional[Tuple[int, int]] = None):
         if not x.is_cuda or x.dtype != torch.float16:
             raise RuntimeError("gtr_b200.GatedLinearAttention runs fp16 on CUDA only (no fallback path)")
         B, T, _ = x.shape
         H = self.num_heads
-        fused = self.qkv_g_gkl_proj(x)
-        q, k, v, g, gkl = fused.split(self.split, dim=-1)
-        gk = self.gk_high_proj(gkl)                               # raw gate logits [B, T, key_dim]
+        if self._folded:
+            q, k, v, g, gk = F.linear(x, self.fused_w, self.fused_b).split(self.split[:4] + (self.key_dim,), dim=-1)
+        else:
+            fused = self.qkv_g_gkl_proj(x)
+            q, k, v, g, gkl = fused.split(self.split, dim=-1)
+            gk = self.gk_high_proj(gkl)                           # raw gate logits [B, T, key_dim]
         view = lambda t: t.unflatten(-1, (H, HEAD_DIM))           # strided views, no copies
         ws, out = self._gla_buffers(B, T, x.device)
         ops.chunk_gla_run_gated(view(q), view(k), view(v), view(gk), view(g), self.g_norm_weight, self.scale,
@@ -186,6 +206,13 @@ class GTRBackbone(nn.Module):
             nn.init.normal_(m.weight, std=0.02)
             if m.bias is not None:
                 nn.init.zeros_(m.bias)
+
+    def convert_to_deploy(self) -> "GTRBackbone":
+        """Inference-time weight transforms (call after the weights are loaded and moved to their device and dtype):
+        folds the low-rank gate head of every block into its fused projection."""
+        for blk in self.blocks:
+            blk.attn.fold_gate_head()
+        return self
 
     def forward(self, img: torch.Tensor) -> List[torch.Tensor]:
         hg, wg = img.shape[-2] // self.patch_size, img.shape[-1] // self.patch_size

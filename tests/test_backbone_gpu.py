@@ -37,6 +37,20 @@ def test_backbone_matches_reference_style_forward(small_model):
         assert m["finite"] and m["rel_l2"] < 1.5e-2, m
 
 
+def test_deploy_form_matches_reference_style_forward(small_model):
+    """convert_to_deploy folds the low-rank gate head into the fused projection: same function, other rounding."""
+    from oracle import backbone_ref, gla_ref
+    img = torch.rand(2, 3, 224, 224, generator=torch.Generator().manual_seed(4))      # 14 x 14 patch grid
+    want = backbone_ref.forward(copy.deepcopy(small_model).float(), img)
+    dev = copy.deepcopy(small_model).half().cuda().convert_to_deploy()
+    assert all(blk.attn._folded for blk in dev.blocks)
+    with torch.no_grad():
+        got = dev(img.half().cuda())
+    for w, g in zip(want, got):
+        m = gla_ref.error_metrics(w, g.float().cpu())
+        assert m["finite"] and m["rel_l2"] < 1.5e-2, m
+
+
 def test_wrong_scan_order_is_detected(small_model):
     """Negative control for the tolerance above."""
     from oracle import backbone_ref, gla_ref
