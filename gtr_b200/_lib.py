@@ -38,7 +38,7 @@ class Args(ctypes.Structure):
 EXPORTS = (
     "gla_b200_forward", "gla_b200_workspace_bytes", "gla_b200_check_status", "gla_b200_rmsnorm_gated",
     "gla_b200_trt_enqueue", "gla_b200_strerror", "gla_b200_last_cuda_error", "gla_b200_version",
-    "gla_b200_forward_static", "gla_b200_selftest_wait_timeout", "gla_b200_swiglu_dwconv",
+    "gla_b200_forward_static", "gla_b200_selftest_wait_timeout", "gla_b200_swiglu_dwconv", "gla_b200_layernorm",
 )
 
 _lib = None
@@ -74,6 +74,8 @@ def lib() -> ctypes.CDLL:
     L.gla_b200_rmsnorm_gated.restype = ctypes.c_int
     L.gla_b200_swiglu_dwconv.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int32] * 4 + [ctypes.c_void_p]
     L.gla_b200_swiglu_dwconv.restype = ctypes.c_int
+    L.gla_b200_layernorm.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int32, ctypes.c_float, ctypes.c_void_p]
+    L.gla_b200_layernorm.restype = ctypes.c_int
     L.gla_b200_trt_enqueue.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32,
                                        ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_int64),
                                        ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_void_p,

@@ -164,8 +164,9 @@ class Block(nn.Module):
         self.mlp = SpatialSwiGLU(dim, hidden_ratio=mlp_ratio, direction=direction)
 
     def forward(self, x: torch.Tensor, grid_hw: Tuple[int, int]) -> torch.Tensor:
-        x = x + self.attn(self.norm1(x), self.direction, grid_hw)
-        return x + self.mlp(self.norm2(x), grid_hw)
+        n1, n2 = self.norm1, self.norm2
+        x = x + self.attn(ops.layernorm(x, n1.weight, n1.bias, n1.eps), self.direction, grid_hw)
+        return x + self.mlp(ops.layernorm(x, n2.weight, n2.bias, n2.eps), grid_hw)
 
 
 class ConvPyramidPatchEmbed(nn.Module):

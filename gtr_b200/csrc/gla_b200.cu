@@ -461,6 +461,22 @@ int gla_b200_swiglu_dwconv(const void* gate, const void* y, const void* weight, 
     return GLA_B200_OK;
 }
 
+int gla_b200_layernorm(const void* x, const void* weight, const void* bias, void* y, int64_t rows, int32_t D, float eps,
+                       void* stream) {
+    if (rows < 0 || D <= 0 || (D & 7) || D > 256 * gla::kLnMaxVec) return GLA_B200_ERR_SHAPE;
+    if (rows == 0) return GLA_B200_OK;
+    if (!x || !weight || !y) return GLA_B200_ERR_NULL;
+    if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || (bias && !aligned16(bias))) return GLA_B200_ERR_ALIGN;
+    const int64_t blocks = (rows + 7) / 8;               // eight warps, one row each
+    if (blocks > 0x7fffffffLL) return GLA_B200_ERR_SHAPE;
+    gla::layernorm_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), static_cast<const __half*>(weight), static_cast<const __half*>(bias),
+        static_cast<__half*>(y), rows, D, eps);
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) { note_cuda("layernorm launch", e); return GLA_B200_ERR_CUDA; }
+    return GLA_B200_OK;
+}
+
 int32_t gla_b200_trt_enqueue(const void* const* inputs, int32_t n_inputs, void* const* outputs, const int64_t* q_dims,
                              float scale, float gk_normalizer, float rms_eps, void* workspace, size_t workspace_bytes,
                              void* stream) {

@@ -113,3 +113,69 @@ __global__ void __launch_bounds__(128, 4) swiglu_dwconv_kernel(const __half* __r
 }
 
 }  // namespace gla
+
+namespace gla {
+
+// LayerNorm over rows of D fp16 values (D a multiple of 8, D <= 2048), affine, fp32 statistics: one warp per row,
+// the row held in registers between the mean, the variance and the output pass, so that x is read once and y written
+// once (the backbone's norms run at a quarter of that with the framework's kernel).
+constexpr int kLnMaxVec = 8;      // 16-byte vectors per lane
+
+__global__ void __launch_bounds__(256) layernorm_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
+                                                             const __half* __restrict__ b, __half* __restrict__ y,
+                                                             long long rows, int D, float eps) {
+    const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int nvec = D >> 3;
+    const uint4* x4 = reinterpret_cast<const uint4*>(x) + row * nvec;
+    float v[kLnMaxVec][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < kLnMaxVec; ++k) {
+        const int i = lane + 32 * k;
+        if (i < nvec) {
+            dw_unpack8(__ldg(x4 + i), v[k]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sum += v[k][e];
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / static_cast<float>(D);
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < kLnMaxVec; ++k) {
+        if (lane + 32 * k < nvec) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float d = v[k][e] - mean;
+                sq = fmaf(d, d, sq);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rstd = rsqrtf(sq / static_cast<float>(D) + eps);
+    uint4* y4 = reinterpret_cast<uint4*>(y) + row * nvec;
+#pragma unroll
+    for (int k = 0; k < kLnMaxVec; ++k) {
+        const int i = lane + 32 * k;
+        if (i < nvec) {
+            float wv[8], bv[8];
+            dw_unpack8(__ldg(reinterpret_cast<const uint4*>(w) + i), wv);
+            if (b != nullptr) dw_unpack8(__ldg(reinterpret_cast<const uint4*>(b) + i), bv);
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float a0 = (v[k][2 * e] - mean) * rstd * wv[2 * e] + (b != nullptr ? bv[2 * e] : 0.f);
+                const float a1 = (v[k][2 * e + 1] - mean) * rstd * wv[2 * e + 1] + (b != nullptr ? bv[2 * e + 1] : 0.f);
+                oh[e] = __floats2half2_rn(a0, a1);
+            }
+            y4[i] = o;
+        }
+    }
+}
+
+}  // namespace gla

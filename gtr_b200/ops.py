@@ -215,3 +215,26 @@ def swiglu_dwconv(gate: torch.Tensor, y: torch.Tensor, weight_taps: torch.Tensor
                                                      bias.data_ptr() if bias is not None else None, out.data_ptr(),
                                                      B, hg, wg, C, ctypes.c_void_p(stream)))
     return out
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LayerNorm over the last dimension of a contiguous float16 CUDA tensor (fp32 statistics); the backbone block's
+    norm1 / norm2 (vit_adapter.py:608-642) in one read and one write.  ``out`` may be ``x``."""
+    if not x.is_cuda or x.dtype != torch.float16 or not x.is_contiguous():
+        raise RuntimeError("x must be a contiguous float16 CUDA tensor")
+    D = x.shape[-1]
+    for t, name in ((weight, "weight"), (bias, "bias")):
+        if t is not None and (t.dtype != torch.float16 or t.numel() != D or not t.is_contiguous() or t.device != x.device):
+            raise RuntimeError(f"{name} must be a contiguous float16 vector of {D} elements on x's device")
+    if out is None:
+        out = torch.empty_like(x)
+    elif out.shape != x.shape or out.dtype != torch.float16 or not out.is_contiguous() or out.device != x.device:
+        raise RuntimeError("out must match x")
+    rows = x.numel() // D if D else 0
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        _lib.check(_lib.lib().gla_b200_layernorm(x.data_ptr(), weight.data_ptr(),
+                                                 bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                                 rows, D, float(eps), ctypes.c_void_p(stream)))
+    return out

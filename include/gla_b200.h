@@ -130,6 +130,13 @@ int gla_b200_rmsnorm_gated(const void* x, const void* g, const void* w, void* y,
 int gla_b200_swiglu_dwconv(const void* gate, const void* y, const void* weight, const void* bias, void* out,
                            int32_t B, int32_t grid_h, int32_t grid_w, int32_t C, void* stream);
 
+/* LayerNorm over rows of D fp16 values with fp32 statistics: y = (x - mean) * rsqrt(var + eps) * weight + bias.
+ * The norms in front of the backbone block's attention and MLP (engine/gtr/backbone/vit_adapter.py:608-642, nn.LayerNorm
+ * with eps 1e-6) in one read and one write of the activations.  D a multiple of 8, at most 2048; bias may be NULL;
+ * y may alias x. */
+int gla_b200_layernorm(const void* x, const void* weight, const void* bias, void* y, int64_t rows, int32_t D, float eps,
+                       void* stream);
+
 /* Shape of GLAPlugin::enqueue (tensorrt_plugin/trt_plugin/gla_plugin.cu:124-163): `inputs` holds
  * q,k,v,gk[,g,rms_w] device pointers, `outputs[0]` the result, dims are those of q [B,T,H,K];
  * the fused epilogue is used iff n_inputs == 6 and rms_eps > 0 (gla_plugin.cu:150).

@@ -49,3 +49,23 @@ def test_rejects_aliasing_and_bad_shapes():
         G.swiglu_dwconv(y, y, taps, None, (4, 5))                  # grid does not match L
     with pytest.raises(RuntimeError):
         G.swiglu_dwconv(y.float(), y, taps, None, (4, 4))
+
+
+@pytest.mark.parametrize("rows,D,with_bias", [(1, 8, True), (37, 768, True), (1000, 128, False), (5, 2048, True), (64, 264, True)])
+def test_layernorm_rows(rows, D, with_bias):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import gtr_b200 as G
+    gen = torch.Generator().manual_seed(rows + D)
+    x = (torch.randn(rows, D, generator=gen) * 2.0 + 0.5).half().cuda()
+    w = (torch.randn(D, generator=gen) * 0.2 + 1.0).half().cuda()
+    b = (torch.randn(D, generator=gen) * 0.1).half().cuda() if with_bias else None
+    ref = F.layer_norm(x.float(), (D,), w.float(), None if b is None else b.float(), 1e-6)
+    y = G.layernorm(x, w, b, 1e-6)
+    assert torch.isfinite(y).all()
+    assert ((y.float() - ref).norm() / ref.norm()).item() < 5e-4          # fp16 output rounding
+    G.layernorm(x, w, b, 1e-6, out=x)                                     # in place
+    assert torch.equal(x, y)
+    with pytest.raises(Exception):
+        G.layernorm(torch.zeros(4, 4096, dtype=torch.float16, device="cuda"), torch.ones(4096, dtype=torch.float16, device="cuda"),
+                    None, 1e-6)
