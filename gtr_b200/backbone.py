@@ -180,6 +180,9 @@ class ConvPyramidPatchEmbed(nn.Module):
         self.proj = nn.Conv2d(chans[-1], embed_dim, 3, 2, padding=1)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        # channels-last through the stem: the convolutions then run without layout conversions around them and
+        # the projection's output already is the dense [B, L, C] token tensor
+        x = x.contiguous(memory_format=torch.channels_last)
         for conv in self.convs:
             x = F.relu(conv(x))
         # tokens as a dense [B, L, C] tensor: a transposed view here would hand its strides on to every
@@ -213,6 +216,7 @@ class GTRBackbone(nn.Module):
         folds the low-rank gate head of every block into its fused projection."""
         for blk in self.blocks:
             blk.attn.fold_gate_head()
+        self.patch_embed.to(memory_format=torch.channels_last)
         return self
 
     def forward(self, img: torch.Tensor) -> List[torch.Tensor]:
