@@ -126,7 +126,9 @@ def scan_order_cases(ref_root: str):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python make_golden.py <path to a checkout of the GTR reference>")
+    ref_root = sys.argv[1]
     np.savez_compressed(os.path.join(HERE, "recurrence_fp64.npz"), **recurrence_cases(ref_root))
     try:
         np.savez_compressed(os.path.join(HERE, "scan_order.npz"), **scan_order_cases(ref_root))
