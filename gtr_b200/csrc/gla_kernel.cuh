@@ -136,7 +136,7 @@ struct Misc {
     uint64_t empty[kNumStages];
     // A barrier may run at most one phase ahead of its slowest waiter.  Barriers whose producer can run further
     // ahead are rings indexed like the resource they guard (stage, or tf32 buffer / score accumulator).
-    uint64_t o_ready[2], o_free[2];
+    uint64_t o_ready[2], o_free[2], o_norm[2];
     uint64_t ops_ready[kNumStages], a16_ready[kNumStages], a_done[2], a_free[2], os_done[2], os_free[2], s16_ready;
     uint32_t tmem_base;
     volatile uint32_t abort;
@@ -700,6 +700,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             mbar_init(smem_u32(&M.os_free[b]), kStateWarps);
             mbar_init(smem_u32(&M.o_ready[b]), kStateWarps);
             mbar_init(smem_u32(&M.o_free[b]), 1);
+            mbar_init(smem_u32(&M.o_norm[b]), kStateWarps);
         }
         mbar_init(smem_u32(&M.s16_ready), kStateWarps);
         M.abort = 0;
@@ -859,52 +860,13 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     warp_arrive(&M.s16_ready, l);
                 }
 
-                // position along the scan of this thread's output row in the pass's first chunk: u, and for
-                // column scans its column cc and row rr inside the column (floor division: u < 0 only for rows
-                // before the start of a reversed ragged chunk, which are never written); fused epilogue only
-                int u = 0, rr = 0, cc = 0;
-                if (!state_only && P.gated) {
-                    const int p0 = it.first_chunk * kChunk;
-                    u = (P.rev ? (P.T - p0 - kChunk) : p0) + static_cast<int>(rho);
-                    if (P.Wc > 1) {
-                        cc = u / P.Hc;
-                        rr = u - cc * P.Hc;
-                        if (rr < 0) { rr += P.Hc; --cc; }
-                    }
-                }
-                // two instantiations of the chunk loop: the fused epilogue keeps 32 more registers alive per thread and
-                // must not weigh on the plain operator
+                // two instantiations of the chunk loop: the fused epilogue's code must not weigh on the plain operator
                 auto run_chunks = [&](auto gated_tag) {
                 constexpr bool kGated = decltype(gated_tag)::value;
                 for (int i = 0; i < it.nchunks; ++i, ++ctr) {
                     // lanes 0-15: output row -> fp16 output tile
                     // lanes 16-31: S <- 2^(G_L) S + kh^T v ; fp16 copy for the next chunk's read-out
                     const uint32_t p = ctr & 1u;
-                    // fused epilogue: the output gate of this thread's row is asked for before the wait, so that the
-                    // global-memory latency is not spent on the chain from one chunk's state to the next
-                    uint4 gt[kGated ? kD / 8 : 1];
-                    bool live = false;
-                    if constexpr (kGated) {
-                        live = !owner && u >= 0 && u < P.T;
-                        if (live) {
-                            // the token read at this row of the chunk follows the same mapping as the TMA boxes
-                            const long long tok = (P.Wc > 1) ? static_cast<long long>(rr) * P.Wc + cc : u;
-                            const uint4* gp = reinterpret_cast<const uint4*>(
-                                P.gate + it.b * P.gate_sb + tok * P.gate_st + it.h * P.gate_sh);
-#pragma unroll
-                            for (int m = 0; m < kD / 8; ++m) gt[m] = __ldg(gp + m);
-                        }
-                        // next chunk: 64 steps further along the scan
-                        if (!P.rev) {
-                            u += kChunk;
-                            rr += kChunk;
-                            while (rr >= P.Hc) { rr -= P.Hc; ++cc; }
-                        } else {
-                            u -= kChunk;
-                            rr -= kChunk;
-                            while (rr < 0) { rr += P.Hc; --cc; }
-                        }
-                    }
                     group_wait(ctx, &M.os_done[p], (ctr >> 1) & 1u, w, 2, kStateThreads);
                     GLA_EV(14);
                     tc_fence_after();
@@ -931,29 +893,20 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             if (owner && !GLA_DBGP(3)) store_row_f16<kD / 8>(base + kOffS16, rho, 0, S);
                             fence_proxy_async_smem();
                             if (i + 1 < it.nchunks) warp_arrive(&M.s16_ready, l);
-                            // y = o * rsqrt(mean(o^2) + eps) * w * silu(gate) on the output rows (lanes 0-15)
-                            if (live) {
-                                float ss = 0.f;
+                            // output rows (lanes 0-15): o * rsqrt(mean(o^2) + eps) goes into the output tile in fp16; the
+                            // score group multiplies by w * silu(gate) in place and hands the tile to the store warp
+                            if (!owner) {
+                                float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                                for (int v = 0; v < kD; ++v) ss = fmaf(S[v], S[v], ss);
+                                for (int v = 0; v < kD; ++v) s4[v & 3] = fmaf(S[v], S[v], s4[v & 3]);
+                                const float ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
                                 const float rinv = P.o_mul * rsqrtf(ss * (P.o_mul * P.o_mul) * (1.f / kD) + P.rms_eps);
-                                const uint4* wp = reinterpret_cast<const uint4*>(P.rms_w);
 #pragma unroll
-                                for (int m = 0; m < kD / 8; ++m) {
-                                    const uint4 g4 = gt[m], w4 = __ldg(wp + m);
-                                    const uint32_t gu[4] = {g4.x, g4.y, g4.z, g4.w}, wu[4] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-                                    for (int q2 = 0; q2 < 4; ++q2) {
-                                        const float2 gf = unpack_half2(gu[q2]), wf = unpack_half2(wu[q2]);
-                                        S[8 * m + 2 * q2] *= rinv * wf.x * silu_f(gf.x);
-                                        S[8 * m + 2 * q2 + 1] *= rinv * wf.y * silu_f(gf.y);
-                                    }
-                                }
+                                for (int v = 0; v < kD; ++v) S[v] *= rinv;
                             }
                             mbar_wait(ctx, &M.o_free[j], ((c2 >> 1) & 1u) ^ 1u);   // tile's previous store has read it
                             if (!owner && !GLA_DBGP(3)) store_row_f16<kD / 8>(base + kOffOut + j * kTileBytes, rho, 0, S);
-                            fence_proxy_async_smem();
-                            warp_arrive(&M.o_ready[j], l);
+                            warp_arrive(&M.o_norm[j], l);
                         } else {
                             if (P.o_mul != 1.f) {         // scale not folded into q (zero, negative or not finite)
                                 const float mul = owner ? 1.f : P.o_mul;
@@ -1018,9 +971,75 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     ctr += it.nchunks;
                     continue;
                 }
+                // fused epilogue: position along the scan of this thread's output row in the chunk: u, and for column
+                // scans its column cc and row rr inside the column (floor division: u < 0 only for rows before the
+                // start of a reversed ragged chunk, which are never written)
+                int u = 0, rr = 0, cc = 0;
+                if (P.gated) {
+                    const int p0 = it.first_chunk * kChunk;
+                    u = (P.rev ? (P.T - p0 - kChunk) : p0) + static_cast<int>(rho);
+                    if (P.Wc > 1) {
+                        cc = u / P.Hc;
+                        rr = u - cc * P.Hc;
+                        if (rr < 0) { rr += P.Hc; --cc; }
+                    }
+                }
+                // fused epilogue, second half: y = (o * rinv) * w * silu(gate) in place on this thread's half row of
+                // output tile (cp & 1), which the state group has filled with the normalised outputs of chunk cp; runs
+                // one chunk behind the scores so that it never sits on the chain from one chunk's state to the next
+                auto gated_epilogue = [&](uint32_t cp, const uint4* gp) {
+                    const uint32_t jb = cp & 1u;
+                    mbar_wait(ctx, &M.o_norm[jb], (cp >> 1) & 1u);
+                    if (gp != nullptr) {       // rows past the end of the sequence are never sent out
+                        const uint4* wp = reinterpret_cast<const uint4*>(P.rms_w + j0);
+                        const uint32_t row = base + kOffOut + jb * kTileBytes + rho * 128u;
+#pragma unroll
+                        for (uint32_t m = 0; m < 4; ++m) {
+                            const uint32_t a = row + (((((j0 >> 3) + m) ^ rho) & 7u) << 4);
+                            const uint4 o4 = ld_shared_v4(a), g4 = __ldg(gp + m), w4 = __ldg(wp + m);
+                            const uint32_t ou[4] = {o4.x, o4.y, o4.z, o4.w}, gu[4] = {g4.x, g4.y, g4.z, g4.w},
+                                           wu[4] = {w4.x, w4.y, w4.z, w4.w};
+                            uint32_t y[4];
+#pragma unroll
+                            for (int q2 = 0; q2 < 4; ++q2) {
+                                const float2 of = unpack_half2(ou[q2]), gf = unpack_half2(gu[q2]), wf = unpack_half2(wu[q2]);
+                                y[q2] = pack_half2(of.x * wf.x * silu_f(gf.x), of.y * wf.y * silu_f(gf.y));
+                            }
+                            st_shared_v4(a, y[0], y[1], y[2], y[3]);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    warp_arrive(&M.o_ready[jb], l);
+                };
+                // two instantiations of the chunk loop, as in the state group: the plain operator's loop carries none of
+                // the fused epilogue's code
+                auto run_scores = [&](auto gated_tag) {
+                constexpr bool kGated = decltype(gated_tag)::value;
+                const uint4* gp_prev = nullptr;
                 for (int i = 0; i < it.nchunks; ++i, ++ctr, ++c2) {
                     const uint32_t s = ctr % kNumStages, b = c2 & 1u;
                     const uint32_t a16 = base + kOffStage + s * kStageBytes + 2 * kTileBytes;
+                    // fused epilogue: this thread's half row of the chunk's output gate is asked for now, into L2 (the
+                    // score group's register budget has no room to hold it)
+                    const uint4* gp = nullptr;
+                    if constexpr (kGated) {
+                        if (u >= 0 && u < P.T) {
+                            // the token read at this row of the chunk follows the same mapping as the TMA boxes
+                            const long long tok = (P.Wc > 1) ? static_cast<long long>(rr) * P.Wc + cc : u;
+                            gp = reinterpret_cast<const uint4*>(
+                                P.gate + it.b * P.gate_sb + tok * P.gate_st + it.h * P.gate_sh + j0);
+                            prefetch_l2(gp);
+                        }
+                        if (!P.rev) {
+                            u += kChunk;
+                            rr += kChunk;
+                            while (rr >= P.Hc) { rr -= P.Hc; ++cc; }
+                        } else {
+                            u -= kChunk;
+                            rr -= kChunk;
+                            while (rr < 0) { rr += P.Hc; --cc; }
+                        }
+                    }
                     group_wait(ctx, &M.a_done[b], (c2 >> 1) & 1u, quad, 3, kScoreThreads);
                     GLA_EV(10);
                     tc_fence_after();
@@ -1039,7 +1058,17 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     fence_proxy_async_smem();
                     warp_arrive(&M.a16_ready[c2 % kNumStages], l);
                     GLA_EV(11);
+                    if constexpr (kGated) {
+                        if (i > 0) gated_epilogue(c2 - 1u, gp_prev);
+                        gp_prev = gp;
+                    }
                 }
+                if constexpr (kGated) {
+                    if (it.nchunks > 0) gated_epilogue(c2 - 1u, gp_prev);
+                }
+                };
+                if (P.gated) run_scores(std::true_type{});
+                else run_scores(std::false_type{});
             }
             __syncthreads();
         }
