@@ -185,7 +185,7 @@ def run_backbone(args, rank, local_rank, world, dist):
     weights, pixels ~ U(0,1).  One CUDA graph per rank; no collective on the data path."""
     from gtr_b200.backbone import GTRBackbone, GraphedBackbone
     dev = torch.device("cuda", local_rank)
-    total_batch = 32
+    total_batch = args.backbone_batch
     if total_batch % world:
         return {"unavailable": f"batch {total_batch} does not divide over {world} ranks"}
     b = total_batch // world
@@ -408,6 +408,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--backbone-steps", type=int, default=5,
                     help="timed steps of the full synthetic backbone (reported under 'backbone'); 0 skips it")
+    ap.add_argument("--backbone-batch", type=int, default=32,
+                    help="images per backbone step over all ranks (32 = the named configuration; smaller for profiling)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     args = ap.parse_args()

@@ -184,7 +184,13 @@ class ConvPyramidPatchEmbed(nn.Module):
         # the projection's output already is the dense [B, L, C] token tensor
         x = x.contiguous(memory_format=torch.channels_last)
         for conv in self.convs:
-            x = F.relu(conv(x))
+            if x.is_cuda:
+                # cuDNN's fused convolution + bias + ReLU: otherwise the bias and the ReLU are two more passes over
+                # the stem's large early feature maps (a strided add and a clamp per stage)
+                x = torch.cudnn_convolution_relu(x, conv.weight, conv.bias, conv.stride, conv.padding, conv.dilation,
+                                                 conv.groups)
+            else:
+                x = F.relu(conv(x))
         # tokens as a dense [B, L, C] tensor: a transposed view here would hand its strides on to every
         # residual sum of the backbone (strided adds, a copy in front of each LayerNorm)
         return self.proj(x).flatten(2).transpose(1, 2).contiguous()
