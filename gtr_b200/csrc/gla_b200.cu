@@ -449,13 +449,16 @@ int gla_b200_swiglu_dwconv(const void* gate, const void* y, const void* weight, 
     if (!aligned16(gate) || !aligned16(y) || !aligned16(weight) || !aligned16(out) || (bias && !aligned16(bias)))
         return GLA_B200_ERR_ALIGN;
     if (out == gate || out == y) return GLA_B200_ERR_ARG;      // neighbours are read after their own output is written
-    const int64_t strips = (grid_w + gla::kDwStrip - 1) / gla::kDwStrip;
-    const int64_t threads = static_cast<int64_t>(B) * grid_h * strips * (C >> 3);
-    const int64_t blocks = (threads + 127) / 128;
-    if (blocks > 0x7fffffffLL) return GLA_B200_ERR_SHAPE;
-    gla::swiglu_dwconv_kernel<<<static_cast<unsigned>(blocks), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(gate), static_cast<const __half*>(y), static_cast<const __half*>(weight),
-        static_cast<const __half*>(bias), static_cast<__half*>(out), B, grid_h, grid_w, C);
+    {
+        const int64_t tiles = static_cast<int64_t>((grid_h + gla::kDwTileR - 1) / gla::kDwTileR) *
+                              ((grid_w + gla::kDwTileC - 1) / gla::kDwTileC);
+        const int64_t blocks = static_cast<int64_t>(B) * tiles * (((C >> 3) + gla::kDwSlab - 1) / gla::kDwSlab);
+        if (blocks > 0x7fffffffLL) return GLA_B200_ERR_SHAPE;
+        gla::swiglu_dwconv_kernel<<<static_cast<unsigned>(blocks), gla::kDwTileThreads, gla::kDwTileSmem,
+                                          static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const __half*>(gate), static_cast<const __half*>(y), static_cast<const __half*>(weight),
+            static_cast<const __half*>(bias), static_cast<__half*>(out), B, grid_h, grid_w, C);
+    }
     cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) { note_cuda("swiglu_dwconv launch", e); return GLA_B200_ERR_CUDA; }
     return GLA_B200_OK;

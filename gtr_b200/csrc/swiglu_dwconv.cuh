@@ -4,19 +4,15 @@
 // form of the reference's SpatialSwiGLU (engine/gtr/backbone/vit_adapter_spatial_swiglu.py:50-60), the chain
 // view/permute -> cuDNN depthwise 3x3 conv -> permute/reshape -> silu -> multiply and the layout copies around it.
 //
-// HBM-bound: gate and y are read once, out is written once (3 * 2 bytes per element); the 3x3 window makes every
-// y element be loaded three times, twice from L2.  A thread owns 8 channels (one 16-byte vector) and a strip of
-// kStrip consecutive grid columns of one grid row; it slides a 3x3 window of vectors along the strip, so each step
-// loads three new vectors (rows r-1, r, r+1 of the next column), one gate vector, and stores one output vector.
-// Consecutive threads hold consecutive channel groups: every access of a warp is 512 contiguous bytes.
+// HBM-bound: gate and y are read once, out is written once (3 * 2 bytes per element).  What limits a direct form
+// (every thread loading its 3x3 window from global memory: 3.4 loads of y per output, two thirds of them L2 hits)
+// is the L2 -> SM path, which moved about 4 TB/s whatever the instruction mix; hence the shared-memory tile below.
 #pragma once
 
 #include <cuda_fp16.h>
 #include <cstdint>
 
 namespace gla {
-
-constexpr int kDwStrip = 16;
 
 __device__ __forceinline__ void dw_unpack8(const uint4& v, float* x) {
     const __half2* h = reinterpret_cast<const __half2*>(&v);
@@ -37,56 +33,98 @@ __device__ __forceinline__ void dw_fma8(float* acc, const uint4& wv, const uint4
 }
 
 // gate, y, out: [B, hg, wg, C] fp16 contiguous; wt: [3][3][C] fp16 (tap-major); bias: [C] fp16 or null.
-__global__ void __launch_bounds__(128, 4) swiglu_dwconv_kernel(const __half* __restrict__ gate, const __half* __restrict__ y,
-                                                            const __half* __restrict__ wt, const __half* __restrict__ bias,
-                                                            __half* __restrict__ out, int B, int hg, int wg, int C) {
-    const int CG = C >> 3;
-    const int nstrips = (wg + kDwStrip - 1) / kDwStrip;
-    const long long total = static_cast<long long>(B) * hg * nstrips * CG;
-    const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (t >= total) return;
-    const int cg = static_cast<int>(t % CG);
-    long long rest = t / CG;
-    const int s = static_cast<int>(rest % nstrips);
-    rest /= nstrips;
-    const int r = static_cast<int>(rest % hg);
-    const int b = static_cast<int>(rest / hg);
-    const int c0 = s * kDwStrip, c1 = min(c0 + kDwStrip, wg);
+// A CTA brings the y tile of kDwTileR x kDwTileC outputs plus its one-cell halo, for a slab of kDwSlab channel groups
+// (8 channels each), into shared memory with cp.async -- every y element crosses the L2 -> SM path 1.4 times -- and
+// each thread (one tile row, one channel group) then slides its 3x3 window of 16-byte vectors along the row out of
+// shared memory.  The whole tile is in flight at once (45 KB per CTA, four CTAs per SM); consecutive threads hold
+// consecutive channel groups, so every global access of a half-warp is 256 contiguous bytes.
+#ifndef DW_TR
+#define DW_TR 8
+#endif
+#ifndef DW_MINB
+#define DW_MINB 4
+#endif
+constexpr int kDwTileR = DW_TR, kDwTileC = 16, kDwSlab = 16;
+constexpr int kDwTileThreads = kDwTileR * kDwSlab;                                   // 128
+constexpr int kDwTilePos = (kDwTileR + 2) * (kDwTileC + 2);                          // 180 positions
+constexpr int kDwTileSmem = kDwTilePos * kDwSlab * 16;                               // 46,080 bytes
 
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    const uint4* w4 = reinterpret_cast<const uint4*>(wt) + cg;          // + tap * CG
+__device__ __forceinline__ void dw_cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+__global__ void __launch_bounds__(kDwTileThreads, DW_MINB) swiglu_dwconv_kernel(
+    const __half* __restrict__ gate, const __half* __restrict__ y, const __half* __restrict__ wt,
+    const __half* __restrict__ bias, __half* __restrict__ out, int B, int hg, int wg, int C) {
+    extern __shared__ __align__(16) unsigned char dw_smem[];
+    const int CG = C >> 3;
+    const int nslab = (CG + kDwSlab - 1) / kDwSlab;
+    const int tiles_c = (wg + kDwTileC - 1) / kDwTileC, tiles_r = (hg + kDwTileR - 1) / kDwTileR;
+    // block -> (b, tile row, tile column, slab), slab fastest: neighbouring CTAs read neighbouring bytes
+    long long rest = blockIdx.x;
+    const int slab = static_cast<int>(rest % nslab); rest /= nslab;
+    const int tc = static_cast<int>(rest % tiles_c); rest /= tiles_c;
+    const int tr = static_cast<int>(rest % tiles_r);
+    const int b = static_cast<int>(rest / tiles_r);
+    const int r0 = tr * kDwTileR, c0 = tc * kDwTileC, cg0 = slab * kDwSlab;
+    const int tid = threadIdx.x;
+    const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(dw_smem));
+    const uint4* y4 = reinterpret_cast<const uint4*>(y);
+    const long long img = static_cast<long long>(b) * hg * wg;
+
+    // ---- fill: position (pr, pc) of the halo tile is grid cell (r0 - 1 + pr, c0 - 1 + pc); zeros outside the grid
+    for (int idx = tid; idx < kDwTilePos * kDwSlab; idx += kDwTileThreads) {
+        const int pos = idx / kDwSlab, ci = idx - pos * kDwSlab;
+        const int pr = pos / (kDwTileC + 2), pc = pos - pr * (kDwTileC + 2);
+        const int r = r0 - 1 + pr, c = c0 - 1 + pc, cg = cg0 + ci;
+        const uint32_t dst = sbase + static_cast<uint32_t>(idx) * 16u;
+        if (r >= 0 && r < hg && c >= 0 && c < wg && cg < CG)
+            dw_cp_async16(dst, y4 + (img + static_cast<long long>(r) * wg + c) * CG + cg);
+        else
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    // ---- this thread: tile row trow, channel group cg; weights and bias while the tile is in flight
+    const int ci = tid % kDwSlab, trow = tid / kDwSlab;
+    const int cg = cg0 + ci, r = r0 + trow;
+    const bool active = cg < CG && r < hg;
+    const int cgc = cg < CG ? cg : CG - 1;
     uint4 wv[9];
 #pragma unroll
-    for (int k = 0; k < 9; ++k) wv[k] = __ldg(w4 + static_cast<long long>(k) * CG);
+    for (int k = 0; k < 9; ++k) wv[k] = __ldg(reinterpret_cast<const uint4*>(wt) + static_cast<long long>(k) * CG + cgc);
     float bv[8];
-    if (bias != nullptr) dw_unpack8(__ldg(reinterpret_cast<const uint4*>(bias) + cg), bv);
+    if (bias != nullptr) dw_unpack8(__ldg(reinterpret_cast<const uint4*>(bias) + cgc), bv);
     else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) bv[i] = 0.f;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (!active) return;
 
-    // vector index of (b, row, col): ((b * hg + row) * wg + col) * CG + cg
-    const long long row_stride = static_cast<long long>(wg) * CG;
-    const long long base = (static_cast<long long>(b) * hg + r) * row_stride + cg;
-    const uint4* y4 = reinterpret_cast<const uint4*>(y);
-    const bool up = r > 0, down = r + 1 < hg;
-    auto load_col = [&](int c, uint4& a, uint4& m, uint4& d) {
-        if (c < 0 || c >= wg) {
-            a = m = d = zero;
-            return;
-        }
-        const long long p = base + static_cast<long long>(c) * CG;
-        a = up ? __ldg(y4 + p - row_stride) : zero;
-        m = __ldg(y4 + p);
-        d = down ? __ldg(y4 + p + row_stride) : zero;
+    auto ld = [&](int pr, int pc) {
+        uint4 v;
+        const uint32_t a = sbase + static_cast<uint32_t>((pr * (kDwTileC + 2) + pc) * kDwSlab + ci) * 16u;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+        return v;
     };
-    uint4 l0, l1, l2, m0, m1, m2, n0, n1, n2;     // window columns c-1 (l), c (m), c+1 (n); rows r-1, r, r+1
-    load_col(c0 - 1, l0, l1, l2);
-    load_col(c0, m0, m1, m2);
-    for (int c = c0; c < c1; ++c) {
-        load_col(c + 1, n0, n1, n2);
-        const long long p = base + static_cast<long long>(c) * CG;
-        const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gate) + p);
+    const long long base = (img + static_cast<long long>(r) * wg) * CG + cg;
+    const uint4* g4 = reinterpret_cast<const uint4*>(gate);
+    uint4* o4 = reinterpret_cast<uint4*>(out);
+    const int ncol = min(kDwTileC, wg - c0);
+    uint4 l0 = ld(trow, 0), l1 = ld(trow + 1, 0), l2 = ld(trow + 2, 0);
+    uint4 m0 = ld(trow, 1), m1 = ld(trow + 1, 1), m2 = ld(trow + 2, 1);
+    // the gate vectors come straight from global memory, asked for two columns ahead of their use
+    const long long pcol = base + static_cast<long long>(c0) * CG;
+    uint4 ga = __ldg(g4 + pcol), gb = ncol > 1 ? __ldg(g4 + pcol + CG) : ga;
+#pragma unroll 1
+    for (int j = 0; j < ncol; ++j) {
+        const uint4 n0 = ld(trow, j + 2), n1 = ld(trow + 1, j + 2), n2 = ld(trow + 2, j + 2);
+        const long long p = pcol + static_cast<long long>(j) * CG;
+        const uint4 gv = ga;
+        ga = gb;
+        if (j + 2 < ncol) gb = __ldg(g4 + p + 2 * static_cast<long long>(CG));
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = bv[i];
@@ -99,14 +137,13 @@ __global__ void __launch_bounds__(128, 4) swiglu_dwconv_kernel(const __half* __r
         __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            // silu(x) = h + h * tanh(h), h = x / 2
-            const float h0 = 0.5f * g[2 * i], h1 = 0.5f * g[2 * i + 1];
+            const float h0 = 0.5f * g[2 * i], h1 = 0.5f * g[2 * i + 1];      // silu(x) = h + h * tanh(h), h = x / 2
             float t0, t1;
             asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(h0));
             asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(h1));
             oh[i] = __floats2half2_rn(fmaf(h0, t0, h0) * acc[2 * i], fmaf(h1, t1, h1) * acc[2 * i + 1]);
         }
-        reinterpret_cast<uint4*>(out)[p] = o;
+        o4[p] = o;
         l0 = m0; l1 = m1; l2 = m2;
         m0 = n0; m1 = n1; m2 = n2;
     }

@@ -16,7 +16,8 @@ def _reference(gate, y, conv_w, bias, hg, wg):
 
 
 @pytest.mark.parametrize("B,hg,wg,C,with_bias", [(2, 8, 8, 64, True), (1, 5, 37, 256, True), (3, 17, 3, 128, False),
-                                                 (1, 1, 1, 8, True), (1, 64, 128, 512, True)])
+                                                 (1, 1, 1, 8, True), (1, 64, 128, 512, True), (2, 9, 18, 200, True),
+                                                 (1, 16, 32, 392, False)])
 def test_matches_conv_silu_product(B, hg, wg, C, with_bias):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
