@@ -94,7 +94,8 @@ class GatedLinearAttention(nn.Module):
                                                self.gk_high_proj.bias.to(W.dtype)]).contiguous(), requires_grad=False)
         self._folded = True
 
-    def forward(self, x: torch.Tensor, direction: int = 0, grid_hw: Optional[Tuple[int, int]] = None):
+    def forward(self, x: torch.Tensor, direction: int = 0, grid_hw: Optional[Tuple[int, int]] = None,
+                residual: Optional[torch.Tensor] = None, keep_residual: bool = True):
         if not x.is_cuda or x.dtype != torch.float16:
             raise RuntimeError("gtr_b200.GatedLinearAttention runs fp16 on CUDA only (no fallback path)")
         B, T, _ = x.shape
@@ -110,7 +111,20 @@ class GatedLinearAttention(nn.Module):
         ops.chunk_gla_run_gated(view(q), view(k), view(v), view(gk), view(g), self.g_norm_weight, self.scale,
                                 self.norm_eps, ws, out, self.gate_logit_normalizer, direction=direction,
                                 grid_hw=grid_hw)
-        return self.o_proj(out.flatten(-2))
+        return _project_add(out.flatten(-2), self.o_proj.weight, residual, keep_residual)
+
+
+def _project_add(inp: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor],
+                 keep_residual: bool) -> torch.Tensor:
+    """``residual + inp @ weight.T`` (or the plain projection without a residual).  With ``keep_residual=False``
+    and autograd off, the sum is the GEMM's own epilogue, accumulated into ``residual`` in place (beta = 1): the
+    residual stream is then read once by the GEMM instead of passing through a separate elementwise add."""
+    if residual is None:
+        return F.linear(inp, weight)
+    if keep_residual or torch.is_grad_enabled() or not residual.is_contiguous():
+        return residual + F.linear(inp, weight)
+    residual.view(-1, residual.shape[-1]).addmm_(inp.reshape(-1, inp.shape[-1]), weight.t())
+    return residual
 
 
 class SpatialSwiGLU(nn.Module):
@@ -145,13 +159,14 @@ class SpatialSwiGLU(nn.Module):
             self._taps_key = key
         return self._taps_cache
 
-    def forward(self, x: torch.Tensor, grid_hw: Tuple[int, int]) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, grid_hw: Tuple[int, int], residual: Optional[torch.Tensor] = None,
+                keep_residual: bool = True) -> torch.Tensor:
         gate = F.linear(x, self.gate_w)
         y = F.linear(x, self.value_w)                              # [B, L, C]
         # depthwise 3x3 conv on the patch grid, bias, silu(gate) and the product in one pass over memory, on
         # tokens in place (the reference views y as a channels-last image for cuDNN and back)
         z = ops.swiglu_dwconv(gate, y, self._taps(), self.dwconv.bias, grid_hw)
-        return self.down_proj(z)
+        return _project_add(z, self.down_proj.weight, residual, keep_residual)
 
 
 class Block(nn.Module):
@@ -163,10 +178,14 @@ class Block(nn.Module):
         self.norm2 = nn.LayerNorm(dim, eps=1e-6)
         self.mlp = SpatialSwiGLU(dim, hidden_ratio=mlp_ratio, direction=direction)
 
-    def forward(self, x: torch.Tensor, grid_hw: Tuple[int, int]) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, grid_hw: Tuple[int, int], keep_input: bool = True) -> torch.Tensor:
+        """``keep_input=False`` lets the block overwrite ``x`` with its result (inference only)."""
         n1, n2 = self.norm1, self.norm2
-        x = x + self.attn(ops.layernorm(x, n1.weight, n1.bias, n1.eps), self.direction, grid_hw)
-        return x + self.mlp(ops.layernorm(x, n2.weight, n2.bias, n2.eps), grid_hw)
+        x = self.attn(ops.layernorm(x, n1.weight, n1.bias, n1.eps), self.direction, grid_hw, residual=x,
+                      keep_residual=keep_input)
+        # x now is this block's own tensor (or the caller's, given up with keep_input=False)
+        return self.mlp(ops.layernorm(x, n2.weight, n2.bias, n2.eps), grid_hw, residual=x,
+                        keep_residual=keep_input and torch.is_grad_enabled())
 
 
 class ConvPyramidPatchEmbed(nn.Module):
@@ -230,7 +249,8 @@ class GTRBackbone(nn.Module):
         x = self.patch_embed(img)
         outs = []
         for i, blk in enumerate(self.blocks):
-            x = blk(x, (hg, wg))
+            # a block may overwrite its input unless that input is one of the returned layers
+            x = blk(x, (hg, wg), keep_input=(i - 1) in self.return_layers)
             if i in self.return_layers:
                 outs.append(x)                                     # canonical token order at every layer
         return outs
