@@ -472,9 +472,17 @@ int gla_b200_layernorm(const void* x, const void* weight, const void* bias, void
     if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || (bias && !aligned16(bias))) return GLA_B200_ERR_ALIGN;
     const int64_t blocks = (rows + 7) / 8;               // eight warps, one row each
     if (blocks > 0x7fffffffLL) return GLA_B200_ERR_SHAPE;
-    gla::layernorm_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(x), static_cast<const __half*>(weight), static_cast<const __half*>(bias),
-        static_cast<__half*>(y), rows, D, eps);
+    const int per_lane = ((D >> 3) + 31) / 32;            // 16-byte vectors per lane
+#define GLA_LN_LAUNCH(V)                                                                                              \
+    gla::layernorm_rows_kernel<V><<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(      \
+        static_cast<const __half*>(x), static_cast<const __half*>(weight), static_cast<const __half*>(bias),          \
+        static_cast<__half*>(y), rows, D, eps)
+    if (per_lane <= 1) GLA_LN_LAUNCH(1);
+    else if (per_lane <= 2) GLA_LN_LAUNCH(2);
+    else if (per_lane <= 3) GLA_LN_LAUNCH(3);
+    else if (per_lane <= 4) GLA_LN_LAUNCH(4);
+    else GLA_LN_LAUNCH(gla::kLnMaxVec);
+#undef GLA_LN_LAUNCH
     cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) { note_cuda("layernorm launch", e); return GLA_B200_ERR_CUDA; }
     return GLA_B200_OK;

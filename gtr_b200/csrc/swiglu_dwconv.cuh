@@ -156,8 +156,11 @@ namespace gla {
 // LayerNorm over rows of D fp16 values (D a multiple of 8, D <= 2048), affine, fp32 statistics: one warp per row,
 // the row held in registers between the mean, the variance and the output pass, so that x is read once and y written
 // once (the backbone's norms run at a quarter of that with the framework's kernel).
-constexpr int kLnMaxVec = 8;      // 16-byte vectors per lane
+// kVec = 16-byte vectors per lane, chosen by the host from D: a narrow row must not pay for the registers of the
+// widest one (occupancy is what keeps enough loads in flight here).
+constexpr int kLnMaxVec = 8;
 
+template <int kVec>
 __global__ void __launch_bounds__(256) layernorm_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
                                                              const __half* __restrict__ b, __half* __restrict__ y,
                                                              long long rows, int D, float eps) {
@@ -166,10 +169,10 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const __half* __res
     if (row >= rows) return;
     const int nvec = D >> 3;
     const uint4* x4 = reinterpret_cast<const uint4*>(x) + row * nvec;
-    float v[kLnMaxVec][8];
+    float v[kVec][8];
     float sum = 0.f;
 #pragma unroll
-    for (int k = 0; k < kLnMaxVec; ++k) {
+    for (int k = 0; k < kVec; ++k) {
         const int i = lane + 32 * k;
         if (i < nvec) {
             dw_unpack8(__ldg(x4 + i), v[k]);
@@ -182,7 +185,7 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const __half* __res
     const float mean = sum / static_cast<float>(D);
     float sq = 0.f;
 #pragma unroll
-    for (int k = 0; k < kLnMaxVec; ++k) {
+    for (int k = 0; k < kVec; ++k) {
         if (lane + 32 * k < nvec) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -196,7 +199,7 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const __half* __res
     const float rstd = rsqrtf(sq / static_cast<float>(D) + eps);
     uint4* y4 = reinterpret_cast<uint4*>(y) + row * nvec;
 #pragma unroll
-    for (int k = 0; k < kLnMaxVec; ++k) {
+    for (int k = 0; k < kVec; ++k) {
         const int i = lane + 32 * k;
         if (i < nvec) {
             float wv[8], bv[8];
