@@ -109,13 +109,16 @@ int num_chunks(int T) { return (T + gla::kChunk - 1) / gla::kChunk; }
 // output pass plus about half of that for the state-only pre-pass every segment but the last
 // needs.  One segment per sequence avoids the pre-pass but leaves slots idle when there are few
 // sequences; many segments fill the machine but pay the pre-pass and round up to whole rounds.
-int auto_chunks_per_segment(int NT, int nseq, int slots) {
+int auto_chunks_per_segment(int NT, int nseq, int slots, size_t workspace_bytes) {
     int best_cps = NT;
     double best = 1e300;
     for (int cps = NT; cps >= 1; --cps) {
         const int ns = (NT + cps - 1) / cps;
         if (ns > 1 && cps < kMinAutoCps) break;
         if (cps != (NT + ns - 1) / ns) continue;               // only the balanced split for each segment count
+        // a split whose scratch does not fit the caller's workspace is not a candidate: the policy then settles
+        // for a coarser one (one segment per sequence needs next to nothing)
+        if (ns > 1 && ws_layout(static_cast<size_t>(nseq), static_cast<size_t>(ns)).total > workspace_bytes) continue;
         const long items = static_cast<long>(nseq) * ns;
         const long rounds = (items + slots - 1) / slots;
         const double per_item = cps * (1.0 + (ns > 1 ? 0.5 * (ns - 1) / ns : 0.0)) + (ns > 1 ? 1.0 : 0.0);
@@ -206,8 +209,9 @@ int resolve_strides(const int64_t in[3], int T, int H, int D, int64_t out[3]) {
 }
 
 // ---- standalone RMSNorm * w * silu(gate), rows of 64 fp16 --------------------------------
-__global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __half* __restrict__ x, const __half* __restrict__ g,
-                                                            const __half* __restrict__ wgt, __half* __restrict__ y,
+// y may alias x (in-place use): x is read with plain loads and neither pointer is declared restrict.
+__global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __half* x, const __half* __restrict__ g,
+                                                            const __half* __restrict__ wgt, __half* y,
                                                             int64_t rows, float eps) {
     // 8 lanes per row, 8 fp16 (16 bytes) per lane; a warp covers 4 consecutive rows = 512 contiguous bytes
     const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
@@ -217,7 +221,7 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __half* __rest
     uint4 xr = make_uint4(0, 0, 0, 0), gr = xr;
     const uint4 wr = __ldg(reinterpret_cast<const uint4*>(wgt) + sub);
     if (live) {
-        xr = __ldg(reinterpret_cast<const uint4*>(x + row * 64) + sub);
+        xr = *(reinterpret_cast<const uint4*>(x + row * 64) + sub);
         gr = __ldg(reinterpret_cast<const uint4*>(g + row * 64) + sub);
     }
     const uint32_t* xp = &xr.x;
@@ -246,6 +250,47 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __half* __rest
     if (live) *(reinterpret_cast<uint4*>(y + row * 64) + sub) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// Scratch for gla_b200_forward_static: forward without any caller-provided or allocated scratch.
+//
+// For hosts that must not touch the device allocator when they call the operator: an inference
+// server that handed all device memory to its own pool at start-up (a cudaMalloc there fails or
+// stalls every stream of the process), a plugin whose framework gives it no workspace, or a
+// real-time loop whose memory budget was fixed before it started.  The kernel's scratch (ticket,
+// status word, per-segment flags, segment aggregates and inclusive states) then lives in the array
+// below, which every GPU that loads this library holds until the process exits.
+//
+// In host code the array's name is only a handle, not a device address, so the address is looked
+// up with cudaGetSymbolAddress, once per device and with that device current.  That happens in the
+// first call on a device: make that call before any stream capture.
+// All calls share the one array per device; it keeps the previous call's contents.  The words that
+// must start at zero (ticket, status, flags) are cleared on the stream at the start of every call;
+// everything else is written before it is read.  Two calls that overlap on the same GPU (different
+// streams, or graph branches) would race on the array: serialise them.
+static __device__ __align__(256) unsigned char g_static_scratch[GLA_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+void* g_static_ptr[64] = {nullptr};
+
+// Device address of the built-in array on the current device (looked up on first use).
+int static_scratch(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { note_cuda("cudaGetDevice", e); return GLA_B200_ERR_CUDA; }
+    if (dev < 0 || dev >= 64) return GLA_B200_ERR_DEVICE;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);      // address on the current device
+        if (e != cudaSuccess || p == nullptr) { note_cuda("cudaGetSymbolAddress", e); return GLA_B200_ERR_CUDA; }
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return GLA_B200_OK;
+}
 }  // namespace
 
 extern "C" {
@@ -297,7 +342,19 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     if (gated && (!aligned16(a->out_gate) || !aligned16(a->rms_weight))) return GLA_B200_ERR_ALIGN;
     if (gated && !(a->rms_eps >= 0.f)) return GLA_B200_ERR_ARG;
 #endif
-    if (static_cast<int64_t>(a->B) * a->T * a->H == 0) return GLA_B200_OK;   // nothing to do
+    if (static_cast<int64_t>(a->B) * a->T * a->H == 0) {
+        // nothing to compute; an empty sequence leaves the state as it came in
+        const size_t state_bytes = static_cast<size_t>(a->B) * a->H * gla::kD * gla::kD * sizeof(float);
+        if (a->final_state && state_bytes) {
+            if (!aligned16(a->final_state) || (a->initial_state && !aligned16(a->initial_state))) return GLA_B200_ERR_ALIGN;
+            cudaStream_t st = static_cast<cudaStream_t>(stream_v);
+            cudaError_t e0 = a->initial_state
+                                 ? cudaMemcpyAsync(a->final_state, a->initial_state, state_bytes, cudaMemcpyDeviceToDevice, st)
+                                 : cudaMemsetAsync(a->final_state, 0, state_bytes, st);
+            if (e0 != cudaSuccess) { note_cuda("final state of an empty sequence", e0); return GLA_B200_ERR_CUDA; }
+        }
+        return GLA_B200_OK;
+    }
     if (!a->q || !a->k || !a->v || !a->g || !a->o) return GLA_B200_ERR_NULL;
     if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->g) || !aligned16(a->o) ||
         (a->initial_state && !aligned16(a->initial_state)) || (a->final_state && !aligned16(a->final_state)))
@@ -334,14 +391,10 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     // segmentation
     const int NT = num_chunks(a->T);
     const int nseq = a->B * a->H;
-    int slots = gla::kCtasPerSm * di.sms;
-    if (const char* e = getenv("GLA_B200_MAX_CTAS")) {   // tuning aid: cap the persistent grid
-        const int cap = atoi(e);
-        if (cap > 0 && cap < slots) slots = cap;
-    }
+    const int slots = gla::kCtasPerSm * di.sms;
     int cps;
     if (a->segments > 0) cps = a->segments;
-    else cps = auto_chunks_per_segment(NT, nseq, slots);
+    else cps = auto_chunks_per_segment(NT, nseq, slots, a->workspace ? a->workspace_bytes : 0);
     if (cps > NT) cps = NT;
     const int NS = (NT + cps - 1) / cps;
     const WsLayout L = ws_layout(static_cast<size_t>(nseq), static_cast<size_t>(NS));
@@ -398,7 +451,11 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
 }
 
 int gla_b200_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint32_t limit_us, void* stream_v) {
-    if (!workspace) return GLA_B200_ERR_NULL;
+    if (!workspace) {          // the built-in array of gla_b200_forward_static
+        const int rc = static_scratch(&workspace);
+        if (rc != GLA_B200_OK) return rc;
+        workspace_bytes = GLA_B200_STATIC_SCRATCH_BYTES;
+    }
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < 512) return GLA_B200_ERR_WORKSPACE;
     if (limit_us == 0 || limit_us > 1000000u) return GLA_B200_ERR_ARG;      // a self-test never waits longer than 1 s
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
@@ -416,7 +473,12 @@ int gla_b200_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint
 }
 
 int gla_b200_check_status(const void* workspace, void* stream) {
-    if (!workspace) return GLA_B200_ERR_NULL;
+    if (!workspace) {          // the built-in array of gla_b200_forward_static on the current device
+        void* p = nullptr;
+        const int rc = static_scratch(&p);
+        if (rc != GLA_B200_OK) return rc;
+        workspace = p;
+    }
     uint32_t ctrl[2] = {0, 0};
     cudaError_t e = cudaMemcpyAsync(ctrl, workspace, sizeof(ctrl), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
     if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
@@ -514,50 +576,16 @@ int32_t gla_b200_trt_enqueue(const void* const* inputs, int32_t n_inputs, void* 
 
 }  // extern "C"
 
-// ---------------------------------------------------------------------------------------------
-// Forward without any caller-provided or allocated scratch.
-//
-// For hosts that must not touch the device allocator when they call the operator: an inference
-// server that handed all device memory to its own pool at start-up (a cudaMalloc there fails or
-// stalls every stream of the process), a plugin whose framework gives it no workspace, or a
-// real-time loop whose memory budget was fixed before it started.  The kernel's scratch (ticket,
-// status word, per-segment flags, segment aggregates and inclusive states) then lives in the array
-// below, which every GPU that loads this library holds until the process exits.
-//
-// In host code the array's name is only a handle, not a device address, so the address is looked
-// up with cudaGetSymbolAddress, once per device and with that device current.  That happens in the
-// first call on a device: make that call before any stream capture.
-// All calls share the one array per device; it keeps the previous call's contents.  The words that
-// must start at zero (ticket, status, flags) are cleared on the stream at the start of every call;
-// everything else is written before it is read.  Two calls that overlap on the same GPU (different
-// streams, or graph branches) would race on the array: serialise them.
-static __device__ __align__(256) unsigned char g_static_scratch[GLA_B200_STATIC_SCRATCH_BYTES];
-
-namespace {
-std::mutex g_static_mu;
-void* g_static_ptr[64] = {nullptr};
-}  // namespace
-
 extern "C" int gla_b200_forward_static(const gla_b200_args* a, void* stream) {
     if (!a) return GLA_B200_ERR_NULL;
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) { note_cuda("cudaGetDevice", e); return GLA_B200_ERR_CUDA; }
-    if (dev < 0 || dev >= 64) return GLA_B200_ERR_DEVICE;
     void* ptr = nullptr;
-    {
-        std::lock_guard<std::mutex> lock(g_static_mu);
-        if (g_static_ptr[dev] == nullptr) {
-            void* p = nullptr;
-            e = cudaGetSymbolAddress(&p, g_static_scratch);      // address on the current device
-            if (e != cudaSuccess || p == nullptr) { note_cuda("cudaGetSymbolAddress", e); return GLA_B200_ERR_CUDA; }
-            g_static_ptr[dev] = p;
-        }
-        ptr = g_static_ptr[dev];
-    }
+    const int rc0 = static_scratch(&ptr);
+    if (rc0 != GLA_B200_OK) return rc0;
     gla_b200_args b = *a;
     b.workspace = ptr;
     b.workspace_bytes = GLA_B200_STATIC_SCRATCH_BYTES;
+    // The automatic policy only considers segmentations whose scratch fits the array; only an explicit
+    // `segments` can ask for more than it holds.
     const int rc = gla_b200_forward(&b, stream);
     return rc == GLA_B200_ERR_WORKSPACE ? GLA_B200_ERR_STATIC_SCRATCH : rc;
 }

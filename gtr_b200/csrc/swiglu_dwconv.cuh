@@ -160,9 +160,10 @@ namespace gla {
 // widest one (occupancy is what keeps enough loads in flight here).
 constexpr int kLnMaxVec = 8;
 
+// y may alias x (in-place use): x is read with plain loads and neither pointer is declared restrict.
 template <int kVec>
-__global__ void __launch_bounds__(256) layernorm_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
-                                                             const __half* __restrict__ b, __half* __restrict__ y,
+__global__ void __launch_bounds__(256) layernorm_rows_kernel(const __half* x, const __half* __restrict__ w,
+                                                             const __half* __restrict__ b, __half* y,
                                                              long long rows, int D, float eps) {
     const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -175,7 +176,7 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const __half* __res
     for (int k = 0; k < kVec; ++k) {
         const int i = lane + 32 * k;
         if (i < nvec) {
-            dw_unpack8(__ldg(x4 + i), v[k]);
+            dw_unpack8(x4[i], v[k]);
 #pragma unroll
             for (int e = 0; e < 8; ++e) sum += v[k][e];
         }

@@ -97,8 +97,11 @@ int gla_b200_forward(const gla_b200_args* args, void* stream);
  * The first call on a device looks up the array's device address; issue it before any stream
  * capture.  The array is shared by all calls on that GPU and keeps the last call's contents (the
  * words that must be zero are cleared at the start of each call), so calls that overlap on one GPU
- * race: run them one after another.  Problems whose segmentation needs more than the array return
- * GLA_B200_ERR_STATIC_SCRATCH; every automatic segmentation on a 148-SM GPU fits. */
+ * race: run them one after another.  The automatic segmentation (`segments` = 0) only considers splits whose
+ * scratch fits the array and settles for a coarser one otherwise (one work item per sequence needs no
+ * scratch beyond the control words), so it never fails for size; an explicit `segments` that needs more
+ * than the array returns GLA_B200_ERR_STATIC_SCRATCH.  A time-out inside such a call is read with
+ * gla_b200_check_status(NULL, stream). */
 #define GLA_B200_STATIC_SCRATCH_BYTES (24u << 20)
 int gla_b200_forward_static(const gla_b200_args* args, void* stream);
 
@@ -107,12 +110,15 @@ size_t gla_b200_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_t K, int3
 
 /* Reads the device status word of a workspace after synchronising `stream`:
  * 0, or GLA_B200_ERR_TIMEOUT when a bounded wait expired during the last forward.
+ * `workspace` == NULL reads the status of the current device's built-in array, i.e. of the last
+ * gla_b200_forward_static call there.
  * The reference has no counterpart (its waits are unbounded, gla_chunk.cuh:1229-1233). */
 int gla_b200_check_status(const void* workspace, void* stream);
 
 /* Exercises the kernel's bounded waits without any real work: one warp waits on a barrier and on a
  * flag that nothing ever completes, with a limit of `limit_us` microseconds (<= 1 s).  Afterwards
  * gla_b200_check_status(workspace) must report GLA_B200_ERR_TIMEOUT and the context stays usable.
+ * `workspace` == NULL runs the test on the built-in array of gla_b200_forward_static.
  * No counterpart in the reference, whose device-side waits are unbounded. */
 int gla_b200_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint32_t limit_us, void* stream);
 
