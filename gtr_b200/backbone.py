@@ -236,6 +236,67 @@ class GTRBackbone(nn.Module):
             if m.bias is not None:
                 nn.init.zeros_(m.bias)
 
+    @torch.no_grad()
+    def load_reference_state_dict(self, sd, prefix: str = "backbone._model.") -> "GTRBackbone":
+        """Take the weights of the reference's ``ViTAdapterSpatialSwiGLU`` (its ``state_dict()``; the ViT sits under
+        ``backbone._model.``), in training form or after its ``convert_to_deploy``:
+
+        * stem: ``convs.i.conv`` + ``convs.i.norm`` (BatchNorm, folded here like
+          engine/gtr/backbone/vit_adapter.py:145-152) or the already folded ``convs.i.conv_bn_fused``;
+        * attention: ``q_proj, k_proj, v_proj, g_proj, gk_proj.0`` are stacked into the fused projection
+          (vit_adapter.py:338-374), ``gk_proj.1`` is the gate head, ``g_norm_swish_gate.weight`` the norm weight;
+        * MLP: ``gate_proj`` is split into its gate and value halves (vit_adapter_spatial_swiglu.py:36-48) and the
+          depthwise kernel, which the reference applies on the grid as block i sees it, is re-oriented for the
+          canonical grid (``oriented_dwconv_weight``)."""
+        get = lambda name: torch.as_tensor(sd[prefix + name])
+        has = lambda name: (prefix + name) in sd
+        dst = self.state_dict()
+
+        def put(name, value):
+            dst[name].copy_(value.to(dst[name].dtype))
+
+        for i in range(len(self.patch_embed.convs)):
+            base = f"patch_embed.convs.{i}."
+            if has(base + "conv_bn_fused.weight"):
+                w, b = get(base + "conv_bn_fused.weight"), get(base + "conv_bn_fused.bias")
+            else:
+                w = get(base + "conv.weight").float()
+                gamma, beta = get(base + "norm.weight").float(), get(base + "norm.bias").float()
+                mean, var = get(base + "norm.running_mean").float(), get(base + "norm.running_var").float()
+                std = (var + 1e-5).sqrt()
+                w, b = w * (gamma / std).reshape(-1, 1, 1, 1), beta - mean * gamma / std
+            put(f"patch_embed.convs.{i}.weight", w)
+            put(f"patch_embed.convs.{i}.bias", b)
+        put("patch_embed.proj.weight", get("patch_embed.proj.weight"))
+        put("patch_embed.proj.bias", get("patch_embed.proj.bias"))
+        for i, blk in enumerate(self.blocks):
+            b = f"blocks.{i}."
+            for n in ("norm1.weight", "norm1.bias", "norm2.weight", "norm2.bias", "attn.o_proj.weight",
+                      "mlp.down_proj.weight"):
+                put(b + n, get(b + n))
+            a = b + "attn."
+            if has(a + "qkv_g_gkl_proj.weight"):
+                put(a + "qkv_g_gkl_proj.weight", get(a + "qkv_g_gkl_proj.weight"))
+                put(a + "gk_high_proj.weight", get(a + "gk_high_proj.weight"))
+                put(a + "gk_high_proj.bias", get(a + "gk_high_proj.bias"))
+            else:
+                put(a + "qkv_g_gkl_proj.weight", torch.cat([get(a + n + ".weight") for n in
+                                                           ("q_proj", "k_proj", "v_proj", "g_proj", "gk_proj.0")]))
+                put(a + "gk_high_proj.weight", get(a + "gk_proj.1.weight"))
+                put(a + "gk_high_proj.bias", get(a + "gk_proj.1.bias"))
+            put(a + "g_norm_weight", get(a + "g_norm_swish_gate.weight"))
+            m = b + "mlp."
+            if has(m + "gate_proj.weight"):
+                gate_w, value_w = get(m + "gate_proj.weight").chunk(2, dim=0)
+            else:
+                gate_w, value_w = get(m + "gate_w"), get(m + "value_w")
+            put(m + "gate_w", gate_w)
+            put(m + "value_w", value_w)
+            blk.mlp.load_reference_dwconv(get(m + "dwconv.weight").to(blk.mlp.dwconv.weight),
+                                          get(m + "dwconv.bias").to(blk.mlp.dwconv.bias))
+            blk.attn._folded = False
+        return self
+
     def convert_to_deploy(self) -> "GTRBackbone":
         """Inference-time weight transforms (call after the weights are loaded and moved to their device and dtype):
         folds the low-rank gate head of every block into its fused projection."""

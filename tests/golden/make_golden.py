@@ -12,6 +12,15 @@ What is executed from the reference (imported, never copied):
   * engine/gtr/backbone/vit_adapter_spatial_swiglu.py : `_apply_bid_scan` is applied to an
     index sequence to record the token order each of the first four layers sees.
 
+  * engine/gtr/backbone/vit_adapter_spatial_swiglu.py : `ViTAdapterSpatialSwiGLU` itself (four blocks, dim 128,
+    two heads, ffn_ratio 6, `multi_layer_same_res`), in eval mode on the CPU in fp32, once with expand_k = 1.0
+    (head K = 64) and once with expand_k = 0.5 (head K = 32, what the released configs use).  Two names that the
+    reference binds to Triton kernels are re-bound first, because Triton does not run on a CPU:
+    `vit_adapter.chunk_gla` to the reference's own float64 recurrence (`test_gla._recurrence_fp64`), and
+    `FusedRMSNormGated.forward` to x * rsqrt(mean(x^2) + eps) * w * silu(g) (what test_gla.py:138-139 and
+    tensorrt_plugin/gtr_onnx_patches.py:94-96 state).  Weights are random, rounded to fp16 so that the fixture can
+    store them in half the space; the fixture holds the state dict, the input and the three returned feature maps.
+
     python tests/golden/make_golden.py /path/to/GTR
 """
 from __future__ import annotations
@@ -125,6 +134,61 @@ def scan_order_cases(ref_root: str):
     return out
 
 
+def backbone_cases(ref_root: str, expand_k: float):
+    """Run the reference backbone on the CPU; returns {name: array} with weights (fp16), input and outputs."""
+    head_k = int(128 * expand_k) // 2
+    ref_test = load_reference_test_module(ref_root, head_k)      # K, V constants of its recurrence
+    recurrence = ref_test._recurrence_fp64
+    for name in [n for n in sys.modules if n == "fla" or n.startswith("fla.")]:
+        if isinstance(sys.modules[name], _Anything):
+            del sys.modules[name]
+    sys.path.insert(0, ref_root)
+    for name in ("faster_coco_eval", "faster_coco_eval.core", "faster_coco_eval.core.mask", "calflops"):
+        if name not in sys.modules:
+            _stub(name, COCO=object, COCOeval_faster=object, calculate_flops=None)
+    try:
+        va = importlib.import_module("engine.gtr.backbone.vit_adapter")
+        mod = importlib.import_module("engine.gtr.backbone.vit_adapter_spatial_swiglu")
+    finally:
+        sys.path.pop(0)
+
+    def chunk_gla_cpu(q, k, v, g, initial_state=None, output_final_state=False, cu_seqlens=None, **kw):
+        assert initial_state is None and cu_seqlens is None
+        return recurrence(q, k, v, g).to(q.dtype), None
+
+    def norm_gate_cpu(self, x, g, residual=None, prenorm=False, residual_in_fp32=False):
+        y = x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + self.eps)
+        return y * self.weight * torch.nn.functional.silu(g)
+
+    va.chunk_gla = chunk_gla_cpu
+    va.FusedRMSNormGated.forward = norm_gate_cpu
+    torch.manual_seed(0)
+    model = mod.ViTAdapterSpatialSwiGLU(interaction_indexes=[1, 2, 3], embed_dim=128, num_heads=2, expand_k=expand_k,
+                                        ffn_ratio=6, depth=4, multi_layer_same_res=True, skip_weights_warning=True)
+    model.eval()
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        for name, t in model.state_dict().items():
+            if name.endswith("num_batches_tracked"):
+                continue
+            if name.endswith("running_var") or name.endswith("g_norm_swish_gate.weight") or ".norm.weight" in name:
+                t.copy_(torch.rand(t.shape, generator=g) + 0.5)
+            elif name.endswith("running_mean") or name.endswith(".bias"):
+                t.copy_(torch.randn(t.shape, generator=g) * (1.0 if "gk_proj" in name else 0.1))
+            t.copy_(t.half().float())                        # the fixture stores fp16
+    img = torch.rand(2, 3, 192, 192, generator=g).half().float()
+    with torch.no_grad():
+        outs = model(img)
+    tag = f"k{head_k}"
+    out = {f"{tag}_img": img.half().numpy()}
+    for i, o in enumerate(outs):
+        out[f"{tag}_out{i}"] = o.float().numpy()
+    for name, t in model.state_dict().items():
+        if not name.endswith("num_batches_tracked"):
+            out[f"{tag}_sd/{name}"] = t.half().numpy()
+    return out
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: python make_golden.py <path to a checkout of the GTR reference>")
@@ -135,6 +199,10 @@ def main():
     except Exception as e:  # the backbone module has heavier imports; report, do not hide
         print("scan-order fixture not generated:", repr(e))
         raise
+    bb = {}
+    for expand_k in (1.0, 0.5):
+        bb.update(backbone_cases(ref_root, expand_k))
+    np.savez_compressed(os.path.join(HERE, "backbone_small.npz"), **bb)
 
 
 if __name__ == "__main__":

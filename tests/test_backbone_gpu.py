@@ -37,6 +37,33 @@ def test_backbone_matches_reference_style_forward(small_model):
         assert m["finite"] and m["rel_l2"] < 1.5e-2, m
 
 
+@pytest.mark.parametrize("deploy", [False, True])
+def test_backbone_matches_recorded_outputs_of_the_reference_backbone(deploy):
+    """The fp16 CUDA backbone, loaded with the reference's own state dict, against feature maps the reference's
+    ViTAdapterSpatialSwiGLU produced for the same weights and input (tests/golden/backbone_small.npz, recorded by
+    tests/golden/make_golden.py from the reference run in fp32 on a CPU)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import os
+    import numpy as np
+    from gtr_b200.backbone import GTRBackbone
+    from oracle import gla_ref
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "backbone_small.npz"))
+    sd = {k[len("k64_sd/"):]: torch.from_numpy(z[k]).float() for k in z.files if k.startswith("k64_sd/")}
+    m = GTRBackbone(embed_dim=128, depth=4, num_heads=2, mlp_ratio=6, return_layers=(1, 2, 3)).eval()
+    m.load_reference_state_dict(sd)
+    m = m.half().cuda()
+    if deploy:
+        m.convert_to_deploy()
+    with torch.no_grad():
+        got = m(torch.from_numpy(z["k64_img"]).cuda())
+    for i, g in enumerate(got):
+        ref = torch.from_numpy(z[f"k64_out{i}"])
+        e = gla_ref.error_metrics(ref, g.float().cpu().transpose(1, 2).reshape(ref.shape))
+        # fp16 weights, GEMMs, LayerNorm and convolutions against the reference in fp32
+        assert e["finite"] and e["rel_l2"] < 1.5e-2, (i, e)
+
+
 def test_deploy_form_matches_reference_style_forward(small_model):
     """convert_to_deploy folds the low-rank gate head into the fused projection: same function, other rounding."""
     from oracle import backbone_ref, gla_ref

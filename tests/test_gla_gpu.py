@@ -96,22 +96,68 @@ def test_config2_all_four_scan_orders(G):
         _check(ref, got)
 
 
-def test_config3_high_resolution(G):
+@pytest.mark.parametrize("direction", [0, 1, 2, 3])
+def test_config3_high_resolution(G, direction):
+    """The throughput point of the benchmark (B4 H12 T6400 on an 80 x 80 grid), every scan order it cycles through."""
     from oracle import c_oracle, gla_ref
     q, k, v, g = gla_ref.config_inputs("c3")
-    for d in (0, 2):
-        ref, _ = c_oracle.forward(q, k, v, g, direction=d, grid_hw=(80, 80))
-        got, _ = _run(G, q, k, v, g, direction=d, grid_hw=(80, 80))
-        _check(ref, got)
+    ref, _ = c_oracle.forward(q, k, v, g, direction=direction, grid_hw=(80, 80))
+    got, _ = _run(G, q, k, v, g, direction=direction, grid_hw=(80, 80))
+    _check(ref, got)
 
 
-def test_config5_numerical_stress(G):
+@pytest.mark.parametrize("direction", [0, 1, 2, 3])
+def test_config5_numerical_stress(G, direction):
+    """B2 H8 T8192 on a 64 x 128 grid, inputs ~N(0,3), near-zero decay over long spans, every scan order."""
     from oracle import c_oracle, gla_ref
     q, k, v, g = gla_ref.config_inputs("c5")
-    ref, _ = c_oracle.forward(q, k, v, g, grid_hw=(64, 128))
-    got, _ = _run(G, q, k, v, g, grid_hw=(64, 128))
-    m = _check(ref, got, relative_abs=True)
-    assert m["max_abs"] / m["ref_max"] <= 1e-3
+    ref, _ = c_oracle.forward(q, k, v, g, direction=direction, grid_hw=(64, 128))
+    got, _ = _run(G, q, k, v, g, direction=direction, grid_hw=(64, 128))
+    m = gla_ref.error_metrics(ref, got)
+    print(f"config 5 direction {direction}: max_abs {m['max_abs']:.4g} at ref_max {m['ref_max']:.4g}, "
+          f"rel_l2 {m['rel_l2']:.3g}")
+    assert m["finite"] and m["rel_l2"] <= REL_L2, m
+    # Outputs reach several hundred here and fp16 values of that size are 0.25 to 0.5 apart, so no fp16 output
+    # can be within 2e-3 of the reference in absolute terms: the bound is applied relative to the largest
+    # reference value, and the absolute error is required to stay below one fp16 spacing at that magnitude.
+    assert m["max_abs"] <= MAX_ABS * m["ref_max"], \
+        f"max-abs {m['max_abs']:.4g} exceeds 2e-3 x the largest reference value {m['ref_max']:.4g} (relative reading)"
+    assert m["max_abs"] / m["ref_max"] <= 1e-3, m
+    assert m["max_abs"] <= 2.0 ** (np.floor(np.log2(m["ref_max"])) - 10), \
+        f"absolute max-abs {m['max_abs']:.4g} exceeds one fp16 spacing at {m['ref_max']:.4g}"
+
+
+@pytest.mark.parametrize("direction", [0, 1, 2, 3])
+def test_the_backbone_blocks_call_at_full_length(G, direction):
+    """The call a backbone block makes on 1024 x 2048 images (64 x 128 patch grid, T = 8192, 12 heads): q, k, v,
+    the raw gate logits (normaliser 16) and the output gate are strided views of one packed projection buffer,
+    and RMSNorm * w * silu(gate) is fused into the operator."""
+    from oracle import c_oracle, gla_ref
+    B, H, grid = 2, 12, (64, 128)
+    T, D = grid[0] * grid[1], 12 * 64
+    gen = torch.Generator().manual_seed(40 + direction)
+    packed = torch.randn(B, T, 5 * D, generator=gen)
+    packed[..., :2 * D] *= 0.125                                  # q, k ~ N(0,1)/8
+    packed = packed.half()
+    w = (torch.rand(64, generator=gen) + 0.5).half()
+    view = lambda i: packed[..., i * D:(i + 1) * D].unflatten(-1, (H, 64))
+    q, k, v, gate, logits = (view(i) for i in range(5))
+    # the reference hands its kernel fp16 log gates (vit_adapter.py:506-509 on an fp16 tensor); the kernel here
+    # rounds its own logsigmoid(x)/16 to fp16 as well
+    g = gla_ref.gate_from_logits(logits.float(), 16.0).half()
+    o_ref, _ = c_oracle.forward(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), direction=direction,
+                                grid_hw=grid)
+    y_ref = gla_ref.rmsnorm_swish_gate(o_ref, gate.contiguous(), w, 1e-5)
+    pd = packed.cuda()
+    dview = lambda i: pd[..., i * D:(i + 1) * D].unflatten(-1, (H, 64))
+    ws = G.make_workspace(B, T, H, "cuda")
+    y = torch.full((B, T, H, 64), float("nan"), dtype=torch.float16, device="cuda")
+    G.chunk_gla_run_gated(dview(0), dview(1), dview(2), dview(4), dview(3), w.cuda(), 0.125, 1e-5, ws, y, 16.0,
+                          direction=direction, grid_hw=grid)
+    G.check_status(ws)
+    m = gla_ref.error_metrics(y_ref, y.float().cpu())
+    # the normalised output is of order one: fp16 rounding of y alone is 2^-11 relative per element
+    assert m["finite"] and m["rel_l2"] <= 1.5e-3 and m["max_abs"] <= 2e-2, m
 
 
 def test_matches_reference_fp64_vectors(G, golden_recurrence):

@@ -1,10 +1,15 @@
 """The CPU oracle against vectors produced by the reference's own code (tests/golden/make_golden.py)
 and against the third-party pure-PyTorch recurrence the reference depends on."""
+import os
+
 import numpy as np
 import pytest
 import torch
 
 from oracle import c_oracle, gla_ref
+
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
 def _t(a):
@@ -112,3 +117,29 @@ def test_empty_and_bad_arguments():
     assert o.shape == (1, 0, 2, 64)
     with pytest.raises(ValueError):
         gla_ref.direction_id(7)
+
+
+def _backbone_fixture(tag):
+    z = np.load(os.path.join(GOLDEN, "backbone_small.npz"))
+    sd = {k[len(tag) + 4:]: torch.from_numpy(z[k]).float() for k in z.files if k.startswith(tag + "_sd/")}
+    img = torch.from_numpy(z[tag + "_img"]).float()
+    outs = [torch.from_numpy(z[f"{tag}_out{i}"]) for i in range(3)]
+    return sd, img, outs
+
+
+def test_backbone_oracle_matches_the_reference_backbone():
+    """oracle/backbone_ref.py against outputs of the reference's own ViTAdapterSpatialSwiGLU (four blocks, dim 128,
+    two heads of K = V = 64, ffn_ratio 6; recorded by tests/golden/make_golden.py): pins the stem, the BatchNorm
+    folding, the gate normaliser, norm_eps, the hidden-size rule, the per-block scan orders and the orientation of
+    the depthwise kernels, through the product's load_reference_state_dict."""
+    from gtr_b200.backbone import GTRBackbone
+    from oracle import backbone_ref
+    sd, img, outs = _backbone_fixture("k64")
+    m = GTRBackbone(embed_dim=128, depth=4, num_heads=2, mlp_ratio=6, return_layers=(1, 2, 3)).eval().float()
+    m.load_reference_state_dict(sd)
+    got = backbone_ref.forward(m, img)
+    assert len(got) == 3
+    for ref, o in zip(outs, got):
+        o = o.transpose(1, 2).reshape(ref.shape)                 # the reference returns [B, C, H, W] maps
+        e = gla_ref.error_metrics(ref, o)
+        assert e["finite"] and e["rel_l2"] < 5e-6 and e["max_abs"] < 5e-6, e
