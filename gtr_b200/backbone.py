@@ -19,7 +19,8 @@ block i scans the grid in order ``DIRECTIONS[i % 4]``.  Here tokens never move: 
 (``oriented_dwconv_weight``).  q, k, v and the output gate are strided views of the fused GEMM
 output -- no contiguous copies -- and the gate logits go to the kernel raw (gk_normalizer).
 
-There is no fallback path: fp16 CUDA tensors and head dims K = V = 64 only.
+There is no fallback path: fp16 CUDA tensors, key heads of 32 or 64 channels (expand_k 0.5 or 1 at 64 channels
+per value head) and value heads of 64.
 """
 from __future__ import annotations
 
@@ -53,8 +54,10 @@ class GatedLinearAttention(nn.Module):
         super().__init__()
         self.hidden_size, self.num_heads = hidden_size, num_heads
         self.key_dim, self.value_dim = int(hidden_size * expand_k), int(hidden_size * expand_v)
-        if self.key_dim != num_heads * HEAD_DIM or self.value_dim != num_heads * HEAD_DIM:
-            raise ValueError("gtr_b200 serves head dims K = V = 64 only "
+        self.head_k_dim = self.key_dim // num_heads
+        if (self.key_dim != num_heads * self.head_k_dim or self.head_k_dim not in ops.SUPPORTED_K
+                or self.value_dim != num_heads * HEAD_DIM):
+            raise ValueError(f"gtr_b200 serves key heads of {ops.SUPPORTED_K} and value heads of 64 channels "
                              f"(got K = {self.key_dim / num_heads:g}, V = {self.value_dim / num_heads:g})")
         self.split = (self.key_dim, self.key_dim, self.value_dim, self.value_dim, gate_low_rank_dim)
         self.qkv_g_gkl_proj = nn.Linear(hidden_size, sum(self.split), bias=False)
@@ -63,7 +66,7 @@ class GatedLinearAttention(nn.Module):
         self.o_proj = nn.Linear(self.value_dim, hidden_size, bias=False)
         self.gate_logit_normalizer = float(gate_logit_normalizer)
         self.norm_eps = float(norm_eps)
-        self.scale = HEAD_DIM ** -0.5
+        self.scale = self.head_k_dim ** -0.5
         self._ws_key = None
         self._ws = self._out = None
         self._folded = False
@@ -106,7 +109,7 @@ class GatedLinearAttention(nn.Module):
             fused = self.qkv_g_gkl_proj(x)
             q, k, v, g, gkl = fused.split(self.split, dim=-1)
             gk = self.gk_high_proj(gkl)                           # raw gate logits [B, T, key_dim]
-        view = lambda t: t.unflatten(-1, (H, HEAD_DIM))           # strided views, no copies
+        view = lambda t: t.unflatten(-1, (H, -1))                 # strided views, no copies
         ws, out = self._gla_buffers(B, T, x.device)
         ops.chunk_gla_run_gated(view(q), view(k), view(v), view(gk), view(g), self.g_norm_weight, self.scale,
                                 self.norm_eps, ws, out, self.gate_logit_normalizer, direction=direction,

@@ -132,7 +132,7 @@ int auto_chunks_per_segment(int NT, int nseq, int slots, size_t workspace_bytes)
 struct MapKey {
     const void* ptr[gla::kNumTensors];
     int64_t stride[gla::kNumTensors][3];
-    int B, T, H, Hc, Wc, col;
+    int B, T, H, K, Hc, Wc, col;
     int dev;
     bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
 };
@@ -153,7 +153,10 @@ int build_maps(const MapKey& key, gla::Maps* out) {
         if (key.ptr[t] == nullptr) continue;
         const int64_t sb = key.stride[t][0], st = key.stride[t][1], sh = key.stride[t][2];
         // dims: (d, head, row-in-column, column, batch)
-        const cuuint64_t gdim[5] = {static_cast<cuuint64_t>(gla::kD), static_cast<cuuint64_t>(key.H),
+        // q, k and g of a K = 32 head: the channel dimension keeps its true extent while the box stays 64 wide, so
+        // channels 32..63 of every tile are filled with zeros by the copy engine (out-of-bounds fill)
+        const bool key_side = t == gla::TQ || t == gla::TK || t == gla::TG;
+        const cuuint64_t gdim[5] = {static_cast<cuuint64_t>(key_side ? key.K : gla::kD), static_cast<cuuint64_t>(key.H),
                                     static_cast<cuuint64_t>(key.Hc), static_cast<cuuint64_t>(key.Wc),
                                     static_cast<cuuint64_t>(key.B)};
         const int64_t row_stride = key.col ? st * key.Wc : st;
@@ -301,7 +304,7 @@ const char* gla_b200_strerror(int code) {
     switch (code) {
         case GLA_B200_OK: return "ok";
         case GLA_B200_ERR_NULL: return "a required pointer is NULL";
-        case GLA_B200_ERR_SHAPE: return "unsupported shape (need K = V = 64, B,T,H >= 0, grid_h*grid_w == T)";
+        case GLA_B200_ERR_SHAPE: return "unsupported shape (need K = 32 or 64, V = 64, B,T,H >= 0, grid_h*grid_w == T)";
         case GLA_B200_ERR_ALIGN: return "pointer or stride is not 16-byte aligned";
         case GLA_B200_ERR_DIRECTION: return "direction must be 0 (row), 1 (row reversed), 2 (column) or 3 (column reversed)";
         case GLA_B200_ERR_WORKSPACE: return "workspace is NULL, misaligned or smaller than gla_b200_workspace_bytes()";
@@ -319,7 +322,7 @@ const char* gla_b200_strerror(int code) {
 const char* gla_b200_last_cuda_error(void) { return g_cuda_err; }
 
 size_t gla_b200_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_t K, int32_t V) {
-    if (B < 0 || T < 0 || H < 0 || K != gla::kD || V != gla::kD) return 0;
+    if (B < 0 || T < 0 || H < 0 || (K != 32 && K != gla::kD) || V != gla::kD) return 0;
     const size_t nseq = static_cast<size_t>(B) * H;
     const size_t ns = static_cast<size_t>((num_chunks(T) + kMinAutoCps - 1) / kMinAutoCps);
     return ws_layout(nseq, ns ? ns : 1).total;
@@ -327,7 +330,7 @@ size_t gla_b200_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_t K, int3
 
 int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     if (!a) return GLA_B200_ERR_NULL;
-    if (a->K != gla::kD || a->V != gla::kD || a->B < 0 || a->T < 0 || a->H < 0) return GLA_B200_ERR_SHAPE;
+    if ((a->K != 32 && a->K != gla::kD) || a->V != gla::kD || a->B < 0 || a->T < 0 || a->H < 0) return GLA_B200_ERR_SHAPE;
     if (a->direction < 0 || a->direction > 3) return GLA_B200_ERR_DIRECTION;
     int gh = a->grid_h, gw = a->grid_w;
     if (gh == 0 && gw == 0) { gh = 1; gw = a->T; }
@@ -344,7 +347,7 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
 #endif
     if (static_cast<int64_t>(a->B) * a->T * a->H == 0) {
         // nothing to compute; an empty sequence leaves the state as it came in
-        const size_t state_bytes = static_cast<size_t>(a->B) * a->H * gla::kD * gla::kD * sizeof(float);
+        const size_t state_bytes = static_cast<size_t>(a->B) * a->H * a->K * gla::kD * sizeof(float);
         if (a->final_state && state_bytes) {
             if (!aligned16(a->final_state) || (a->initial_state && !aligned16(a->initial_state))) return GLA_B200_ERR_ALIGN;
             cudaStream_t st = static_cast<cudaStream_t>(stream_v);
@@ -370,7 +373,8 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     for (int t = 0; t < gla::kNumTensors; ++t) {
         key.ptr[t] = ptrs[t];
         if (!ptrs[t]) continue;
-        rc = resolve_strides(strides[t], a->T, a->H, gla::kD, key.stride[t]);
+        const bool key_side = t == gla::TQ || t == gla::TK || t == gla::TG;
+        rc = resolve_strides(strides[t], a->T, a->H, key_side ? a->K : gla::kD, key.stride[t]);
         if (rc != GLA_B200_OK) return rc;
     }
 
@@ -382,7 +386,7 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     rc = device_info(dev, &di);
     if (rc != GLA_B200_OK) return rc;
     const bool col = a->direction >= 2;
-    key.B = a->B; key.T = a->T; key.H = a->H;
+    key.B = a->B; key.T = a->T; key.H = a->H; key.K = a->K;
     key.col = col ? 1 : 0;
     key.Hc = col ? gh : a->T;
     key.Wc = col ? gw : 1;
@@ -408,7 +412,7 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     uint8_t* ws = static_cast<uint8_t*>(a->workspace);
     gla::Params P;
     memset(&P, 0, sizeof(P));
-    P.B = a->B; P.T = a->T; P.H = a->H; P.NT = NT;
+    P.B = a->B; P.T = a->T; P.H = a->H; P.NT = NT; P.K = a->K;
     P.Hc = key.Hc; P.Wc = key.Wc;
     P.rev = a->direction & 1;
     P.NS = NS; P.cps = cps;

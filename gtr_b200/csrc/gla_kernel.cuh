@@ -79,6 +79,10 @@ struct Maps {
 
 struct Params {
     int B, T, H, NT;
+    int K;               // key channels per head, 32 or 64.  A K = 32 head runs as a K = 64 head whose upper 32
+                         // channels are zero: the tensor maps of q, k, g give the channel dimension its true extent,
+                         // so the TMA loads fill channels 32..63 of every tile with zeros without reading anything,
+                         // and state rows 32..63 stay zero
     int Hc, Wc;          // column length / number of columns of the scan (row scans: Hc = T, Wc = 1)
     int rev;             // scan runs from the last token to the first
     int NS, cps;         // segments per sequence, chunks per segment
@@ -748,14 +752,15 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             if (item >= P.num_items) break;
             const ItemInfo it = decode_item(P, item);
             const int npass = it.state_pass ? 2 : 1;
-            const size_t srow = (static_cast<size_t>(it.seq) * kD + my_c) * kD;   // this thread's state row
+            const size_t srow = (static_cast<size_t>(it.seq) * P.K + my_c) * kD;   // this thread's state row
+            const bool real_row = my_c < P.K;      // rows of channels a K = 32 head does not have are zero throughout
             const size_t slot = static_cast<size_t>(it.seq) * P.NS + it.seg;
             float gsum = 0.f;       // log2 of the segment's total decay for channel my_c
 
             auto load_initial = [&]() {
 #pragma unroll
                 for (int x = 0; x < kD; ++x) S[x] = 0.f;
-                if (owner && P.s0 != nullptr) {
+                if (owner && real_row && P.s0 != nullptr) {
                     const float4* src = reinterpret_cast<const float4*>(P.s0 + srow);
 #pragma unroll
                     for (int x = 0; x < kD / 4; ++x) {
@@ -944,7 +949,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     }
                 }
             }
-            if (it.seg == P.NS - 1 && P.sT != nullptr && owner) {
+            if (it.seg == P.NS - 1 && P.sT != nullptr && owner && real_row) {
                 float4* dst = reinterpret_cast<float4*>(P.sT + srow);
 #pragma unroll
                 for (int x4 = 0; x4 < kD / 4; ++x4)

@@ -27,9 +27,10 @@ import torch
 
 from . import _lib
 
-kK = 64
+kK = 64                 # widest key head; SUPPORTED_K lists every key head size served
 kV = 64
 kBT = 64
+SUPPORTED_K = (32, 64)  # the reference extension's own head is K = 32 (gla_chunk.cuh:14); its FLA path takes any K
 
 DIRECTIONS = ("row", "row_rev", "col", "col_rev")
 
@@ -80,9 +81,12 @@ def make_workspace(B: int, T: int, H: int, device) -> torch.Tensor:
 
 def _forward(q, k, v, gk, o, ws, scale, gk_normalizer, direction, grid_hw, initial_state, final_state,
              out_gate=None, rms_w=None, eps=0.0, segments=0, wait_limit=0) -> None:
-    _check_tensor(q, "q", kK)
-    _check_tensor(k, "k", kK, q)
-    _check_tensor(gk, "gk", kK, q)
+    K = q.shape[-1] if isinstance(q, torch.Tensor) and q.dim() == 4 else kK
+    if K not in SUPPORTED_K:
+        raise RuntimeError(f"q: last dim must be one of {SUPPORTED_K}, got {K}")
+    _check_tensor(q, "q", K)
+    _check_tensor(k, "k", K, q)
+    _check_tensor(gk, "gk", K, q)
     _check_tensor(v, "v", kV, q)
     _check_tensor(o, "o", kV, q)
     B, T, H, _ = q.shape
@@ -101,15 +105,15 @@ def _forward(q, k, v, gk, o, ws, scale, gk_normalizer, direction, grid_hw, initi
     for name, s in (("initial_state", initial_state), ("final_state", final_state)):
         if s is None:
             continue
-        if (s.dtype != torch.float32 or tuple(s.shape) != (B, H, kK, kV) or not s.is_contiguous()
+        if (s.dtype != torch.float32 or tuple(s.shape) != (B, H, K, kV) or not s.is_contiguous()
                 or s.device != q.device):
-            raise RuntimeError(f"{name} must be a contiguous float32 [B, H, {kK}, {kV}] tensor on q's device")
+            raise RuntimeError(f"{name} must be a contiguous float32 [B, H, {K}, {kV}] tensor on q's device")
     a.initial_state = initial_state.data_ptr() if initial_state is not None else None
     a.final_state = final_state.data_ptr() if final_state is not None else None
     if not isinstance(ws, torch.Tensor) or not ws.is_cuda or ws.device != q.device or not ws.is_contiguous():
         raise RuntimeError("ws must be a contiguous CUDA tensor on q's device (see make_workspace)")
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
-    a.B, a.T, a.H, a.K, a.V = B, T, H, kK, kV
+    a.B, a.T, a.H, a.K, a.V = B, T, H, K, kV
     if grid_hw is not None:
         a.grid_h, a.grid_w = int(grid_hw[0]), int(grid_hw[1])
     a.direction = _direction_id(direction)
@@ -154,7 +158,7 @@ def chunk_gla(q, k, v, g, scale: Optional[float] = None, initial_state: Optional
         scale = K ** -0.5
     ws = make_workspace(B, T, H, q.device)
     o = torch.empty(B, T, H, kV, dtype=torch.float16, device=q.device)
-    final = torch.empty(B, H, kK, kV, dtype=torch.float32, device=q.device) if output_final_state else None
+    final = torch.empty(B, H, K, kV, dtype=torch.float32, device=q.device) if output_final_state else None
     chunk_gla_run(q, k, v, g, scale, ws, o, gk_normalizer, direction=direction, grid_hw=grid_hw,
                   initial_state=initial_state, final_state=final, segments=segments)
     return o, final

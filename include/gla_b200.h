@@ -6,7 +6,9 @@
  * the GTR reference it stands in for (paths relative to the GTR project root).
  *
  * Tensor contract (reference: engine/gtr/backbone/csrc/gla_torch_ext.cu:15-22,49-66):
- *   q, k, g : fp16 [B, T, H, K]      v, o, out_gate : fp16 [B, T, H, V]      K = V = 64
+ *   q, k, g : fp16 [B, T, H, K]      v, o, out_gate : fp16 [B, T, H, V]      K = 32 or 64, V = 64
+ *   (K = 32, V = 64 is the reference extension's only shape, gla_chunk.cuh:14-16, and what the released GTR
+ *   configs use; K = 64 is what its FLA path serves at expand_k = 1.)
  *   g is the log-space forget gate (<= 0), or raw logits when gk_normalizer > 0, in which
  *   case the kernel applies logsigmoid(g) / gk_normalizer (gla_chunk.cuh:775,788-790).
  *   States are fp32 [B, H, K, V].  All pointers are device pointers, 16-byte aligned.
@@ -34,7 +36,7 @@ extern "C" {
 
 #define GLA_B200_VERSION 1
 #define GLA_B200_CHUNK 64          /* tokens per chunk; reference kBT, gla_chunk.cuh:16 */
-#define GLA_B200_HEAD_K 64         /* reference kK is 32 (gla_chunk.cuh:14); this build serves K = 64 */
+#define GLA_B200_HEAD_K 64         /* widest key head; K = 32 (reference kK, gla_chunk.cuh:14) is served too */
 #define GLA_B200_HEAD_V 64         /* reference kV, gla_chunk.cuh:15 */
 
 enum gla_b200_direction {

@@ -24,7 +24,7 @@ def _attn(att, x):
     fused = att.qkv_g_gkl_proj(x)
     q, k, v, g, gkl = fused.split(att.split, dim=-1)
     gk = gla_ref.gate_from_logits(att.gk_high_proj(gkl), att.gate_logit_normalizer)
-    r = lambda t: t.reshape(B, T, H, 64)
+    r = lambda t: t.reshape(B, T, H, -1)
     o, _ = gla_ref.chunk_gla(r(q), r(k), r(v), r(gk), scale=att.scale)
     y = gla_ref.rmsnorm_swish_gate(o, r(g), att.g_norm_weight, att.norm_eps)
     return att.o_proj(y.reshape(B, T, -1))

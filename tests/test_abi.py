@@ -48,7 +48,8 @@ def test_args_struct_matches_header_size():
 
 def test_workspace_bytes(L):
     assert L.gla_b200_workspace_bytes(4, 6400, 12, 64, 64) > 0
-    assert L.gla_b200_workspace_bytes(4, 6400, 12, 32, 64) == 0      # K = 32 is not served
+    assert L.gla_b200_workspace_bytes(4, 6400, 12, 32, 64) > 0       # the reference extension's own head size
+    assert L.gla_b200_workspace_bytes(4, 6400, 12, 48, 64) == 0
     assert L.gla_b200_workspace_bytes(-1, 64, 1, 64, 64) == 0
     small = L.gla_b200_workspace_bytes(1, 64, 1, 64, 64)
     big = L.gla_b200_workspace_bytes(8, 8192, 12, 64, 64)
@@ -70,7 +71,7 @@ def _args(**kw):
 
 
 @pytest.mark.parametrize("kw,code", [
-    (dict(K=32), -2), (dict(V=128), -2), (dict(B=-1), -2),
+    (dict(K=48), -2), (dict(K=16), -2), (dict(V=128), -2), (dict(V=32), -2), (dict(B=-1), -2),
     (dict(direction=4), -4), (dict(direction=-1), -4),
     (dict(direction=2), -2),                       # column scan without a grid
     (dict(grid_h=10, grid_w=10), -2),              # grid does not cover T

@@ -37,11 +37,13 @@ def test_backbone_matches_reference_style_forward(small_model):
         assert m["finite"] and m["rel_l2"] < 1.5e-2, m
 
 
+@pytest.mark.parametrize("tag,expand_k", [("k64", 1.0), ("k32", 0.5)])
 @pytest.mark.parametrize("deploy", [False, True])
-def test_backbone_matches_recorded_outputs_of_the_reference_backbone(deploy):
+def test_backbone_matches_recorded_outputs_of_the_reference_backbone(deploy, tag, expand_k):
     """The fp16 CUDA backbone, loaded with the reference's own state dict, against feature maps the reference's
     ViTAdapterSpatialSwiGLU produced for the same weights and input (tests/golden/backbone_small.npz, recorded by
-    tests/golden/make_golden.py from the reference run in fp32 on a CPU)."""
+    tests/golden/make_golden.py from the reference run in fp32 on a CPU), with key heads of 64 channels
+    (expand_k = 1) and of 32 (expand_k = 0.5, the released GTR configurations)."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     import os
@@ -49,16 +51,17 @@ def test_backbone_matches_recorded_outputs_of_the_reference_backbone(deploy):
     from gtr_b200.backbone import GTRBackbone
     from oracle import gla_ref
     z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "backbone_small.npz"))
-    sd = {k[len("k64_sd/"):]: torch.from_numpy(z[k]).float() for k in z.files if k.startswith("k64_sd/")}
-    m = GTRBackbone(embed_dim=128, depth=4, num_heads=2, mlp_ratio=6, return_layers=(1, 2, 3)).eval()
+    sd = {k[len(tag) + 4:]: torch.from_numpy(z[k]).float() for k in z.files if k.startswith(tag + "_sd/")}
+    m = GTRBackbone(embed_dim=128, depth=4, num_heads=2, mlp_ratio=6, return_layers=(1, 2, 3),
+                    expand_k=expand_k).eval()
     m.load_reference_state_dict(sd)
     m = m.half().cuda()
     if deploy:
         m.convert_to_deploy()
     with torch.no_grad():
-        got = m(torch.from_numpy(z["k64_img"]).cuda())
+        got = m(torch.from_numpy(z[tag + "_img"]).cuda())
     for i, g in enumerate(got):
-        ref = torch.from_numpy(z[f"k64_out{i}"])
+        ref = torch.from_numpy(z[f"{tag}_out{i}"])
         e = gla_ref.error_metrics(ref, g.float().cpu().transpose(1, 2).reshape(ref.shape))
         # fp16 weights, GEMMs, LayerNorm and convolutions against the reference in fp32
         assert e["finite"] and e["rel_l2"] < 1.5e-2, (i, e)
@@ -108,6 +111,7 @@ def test_rejects_cpu_and_other_head_dims():
     from gtr_b200.backbone import GatedLinearAttention
     with pytest.raises(ValueError):
         GatedLinearAttention(192, 6, expand_k=0.5)              # K = 16 per head
+    assert GatedLinearAttention(192, 3, expand_k=0.5).head_k_dim == 32      # the released GTR-S shape
     att = GatedLinearAttention(128, 2)
     with pytest.raises(RuntimeError):
         att(torch.zeros(1, 64, 128))

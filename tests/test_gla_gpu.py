@@ -34,7 +34,7 @@ def _run(G, q, k, v, g, *, scale=None, direction=0, grid_hw=None, segments=0, s0
         ws = torch.zeros(ws.numel() * 4, dtype=torch.float32, device=dev)
     o = torch.full((B, T, H, 64), float("nan"), dtype=torch.float16, device=dev) if poison else \
         torch.empty(B, T, H, 64, dtype=torch.float16, device=dev)
-    fs = torch.full((B, H, 64, 64), float("nan"), dtype=torch.float32, device=dev) if final else None
+    fs = torch.full((B, H, K, 64), float("nan"), dtype=torch.float32, device=dev) if final else None
     G.chunk_gla_run(qd, kd, vd, gd, scale, ws, o, gk_normalizer, direction=direction, grid_hw=grid_hw,
                     segments=segments, initial_state=None if s0 is None else s0.to(dev), final_state=fs)
     G.check_status(ws)
@@ -437,3 +437,97 @@ def test_bounded_waits_time_out_cleanly(G):
     G.check_status(ws)                                     # cleared by the new launch
     ref, _ = c_oracle.forward(q, k, v, g)
     _check(ref, o.float().cpu())
+
+
+# ---------------------------------------------------------------------------------------------------------
+# K = 32 key heads, V = 64: the reference extension's only shape (gla_chunk.cuh:14-16) and the released models'.
+
+def test_k32_matches_reference_fp64_vectors(G, golden_recurrence):
+    """The reference's own fp64 recurrence on its own seeded inputs at its own head size."""
+    from oracle import gla_ref
+    Gd = golden_recurrence
+    for gates in ("weak", "strong", "bursts"):
+        q, k, v, g = (torch.from_numpy(np.asarray(Gd[f"k32_{gates}_{n}"])) for n in "qkvg")
+        assert q.shape[-1] == 32 and v.shape[-1] == 64
+        ref = torch.from_numpy(np.asarray(Gd[f"k32_{gates}_o"]))
+        got, _ = _run(G, q, k, v, g)
+        m = gla_ref.error_metrics(ref, got)
+        assert m["finite"] and m["rel_l2"] <= REL_L2, (gates, m)
+
+
+@pytest.mark.parametrize("gate", [10.5, 12.0])
+@pytest.mark.parametrize("j", [0, 7, 23, 63])
+def test_k32_single_term_through_a_strong_gate(G, golden_recurrence, gate, j):
+    want = torch.from_numpy(np.asarray(golden_recurrence[f"k32_hist_{gate:g}_{j}_row"]))
+    T = 192
+    q = torch.zeros(1, T, 1, 32, dtype=torch.float16)
+    k = q.clone()
+    v = torch.zeros(1, T, 1, 64, dtype=torch.float16)
+    g = torch.full_like(q, -0.08)
+    q[0, j + 1, 0, 0], k[0, j, 0, 0], v[0, j] = 16.0, 16.0, 4.0
+    g[0, j + 1, 0, 0] = -gate
+    got, _ = _run(G, q, k, v, g)
+    assert torch.isfinite(got).all()
+    row = got[0, j + 1, 0]
+    assert ((row - want).norm() / want.norm()).item() <= 0.02
+
+
+def test_k32_all_gates_minus_1000(G, golden_recurrence):
+    Gd = golden_recurrence
+    q, k, v = (torch.from_numpy(np.asarray(Gd[f"k32_m1000_{n}"])) for n in "qkv")
+    ref = torch.from_numpy(np.asarray(Gd["k32_m1000_o"]))
+    got, _ = _run(G, q, k, v, torch.full_like(q, -1000.0))
+    from oracle import gla_ref
+    m = gla_ref.error_metrics(ref, got)
+    assert m["finite"] and m["rel_l2"] <= 2e-3, m
+
+
+@pytest.mark.parametrize("direction,grid,segments", [(0, (1, 700), 0), (1, (25, 28), 3), (2, (25, 28), 0),
+                                                     (3, (25, 28), 2), (3, (40, 40), 0)])
+def test_k32_scan_orders_segments_and_states(G, direction, grid, segments):
+    from oracle import c_oracle, gla_ref
+    B, H = 2, 3
+    T = grid[0] * grid[1]
+    q, k, v, g = gla_ref.make_inputs(B, T, H, K=32, seed=30 + direction)
+    s0 = torch.randn(B, H, 32, 64, generator=torch.Generator().manual_seed(3))
+    ref, ref_s = c_oracle.forward(q, k, v, g, direction=direction, grid_hw=grid, initial_state=s0,
+                                  output_final_state=True)
+    got, got_s = _run(G, q, k, v, g, direction=direction, grid_hw=grid, segments=segments, s0=s0, final=True)
+    _check(ref, got, relative_abs=True)
+    assert got_s.shape == (B, H, 32, 64) and torch.isfinite(got_s).all()
+    assert ((got_s - ref_s).norm() / ref_s.norm()).item() < 2e-4
+
+
+def test_k32_released_model_call(G):
+    """What a released GTR block hands the operator (dim 192, 3 heads: q, k and the raw gate logits 32 wide, v and
+    the output gate 64 wide, all views of one packed projection), with the fused RMSNorm * w * silu(gate)."""
+    from oracle import c_oracle, gla_ref
+    B, H, grid, direction = 2, 3, (40, 40), 2
+    T = 1600
+    gen = torch.Generator().manual_seed(77)
+    widths = (H * 32, H * 32, H * 64, H * 64, H * 32)             # q, k, v, output gate, gate logits
+    packed = torch.randn(B, T, sum(widths), generator=gen)
+    packed[..., :2 * H * 32] *= 0.18
+    packed = packed.half()
+    w = (torch.rand(64, generator=gen) + 0.5).half()
+
+    def views(t):
+        out, at = [], 0
+        for wd in widths:
+            out.append(t[..., at:at + wd].unflatten(-1, (H, -1)))
+            at += wd
+        return out
+
+    q, k, v, gate, logits = views(packed)
+    g = gla_ref.gate_from_logits(logits.float(), 16.0).half()
+    o_ref, _ = c_oracle.forward(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), direction=direction,
+                                grid_hw=grid)
+    y_ref = gla_ref.rmsnorm_swish_gate(o_ref, gate.contiguous(), w, 1e-5)
+    dq, dk, dv, dgate, dlogits = views(packed.cuda())
+    ws = G.make_workspace(B, T, H, "cuda")
+    y = torch.full((B, T, H, 64), float("nan"), dtype=torch.float16, device="cuda")
+    G.chunk_gla_run_gated(dq, dk, dv, dlogits, dgate, w.cuda(), 32 ** -0.5, 1e-5, ws, y, 16.0, direction=direction,
+                          grid_hw=grid)
+    G.check_status(ws)
+    m = gla_ref.error_metrics(y_ref, y.float().cpu())
+    assert m["finite"] and m["rel_l2"] <= 1.5e-3, m

@@ -127,15 +127,17 @@ def _backbone_fixture(tag):
     return sd, img, outs
 
 
-def test_backbone_oracle_matches_the_reference_backbone():
+@pytest.mark.parametrize("tag,expand_k", [("k64", 1.0), ("k32", 0.5)])
+def test_backbone_oracle_matches_the_reference_backbone(tag, expand_k):
     """oracle/backbone_ref.py against outputs of the reference's own ViTAdapterSpatialSwiGLU (four blocks, dim 128,
-    two heads of K = V = 64, ffn_ratio 6; recorded by tests/golden/make_golden.py): pins the stem, the BatchNorm
+    two heads with V = 64 and K = 64 or 32, ffn_ratio 6; recorded by tests/golden/make_golden.py): pins the stem, the BatchNorm
     folding, the gate normaliser, norm_eps, the hidden-size rule, the per-block scan orders and the orientation of
     the depthwise kernels, through the product's load_reference_state_dict."""
     from gtr_b200.backbone import GTRBackbone
     from oracle import backbone_ref
-    sd, img, outs = _backbone_fixture("k64")
-    m = GTRBackbone(embed_dim=128, depth=4, num_heads=2, mlp_ratio=6, return_layers=(1, 2, 3)).eval().float()
+    sd, img, outs = _backbone_fixture(tag)
+    m = GTRBackbone(embed_dim=128, depth=4, num_heads=2, mlp_ratio=6, return_layers=(1, 2, 3),
+                    expand_k=expand_k).eval().float()
     m.load_reference_state_dict(sd)
     got = backbone_ref.forward(m, img)
     assert len(got) == 3
