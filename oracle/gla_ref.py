@@ -149,34 +149,8 @@ def rmsnorm_swish_gate(o, gate, w, eps: float):
     return o * torch.rsqrt(o.square().mean(-1, keepdim=True) + eps) * w * F.silu(gate)
 
 
-# ---------------------------------------------------------------------------------------
-# Seeded synthetic inputs with the shapes and value distributions of the benchmark configs.
-# Generated in fp32 on the CPU (so CPU and GPU see identical values), order q, k, v, g.
-# ---------------------------------------------------------------------------------------
-CONFIGS = {
-    # name: (B, H, T, (Hg, Wg), qkv_std, gate)
-    "c1": dict(B=1, H=6, T=1600, grid=(40, 40), std=1.0 / 8, gate=("ls", 0.0, 1.0, 16.0)),
-    "c2": dict(B=8, H=6, T=1600, grid=(40, 40), std=1.0 / 8, gate=("ls", 0.0, 1.0, 16.0)),
-    "c3": dict(B=4, H=12, T=6400, grid=(80, 80), std=1.0 / 8, gate=("ls", 0.0, 1.0, 16.0)),
-    "c5": dict(B=2, H=8, T=8192, grid=(64, 128), std=3.0, gate=("ls", 4.0, 2.0, 1.0)),
-}
-
-
-def make_inputs(B, T, H, K=64, V=64, std=1.0 / 8, gate=("ls", 0.0, 1.0, 16.0), seed=0,
-                dtype=torch.float16):
-    gen = torch.Generator().manual_seed(seed)
-    q = torch.randn(B, T, H, K, generator=gen) * std
-    k = torch.randn(B, T, H, K, generator=gen) * std
-    v = torch.randn(B, T, H, V, generator=gen) * std
-    kind, mean, gstd, norm = gate
-    assert kind == "ls"
-    g = F.logsigmoid(torch.randn(B, T, H, K, generator=gen) * gstd + mean) / norm
-    return tuple(x.to(dtype) for x in (q, k, v, g))
-
-
-def config_inputs(name: str, seed: int = 0, dtype=torch.float16, B=None):
-    c = CONFIGS[name]
-    return make_inputs(B or c["B"], c["T"], c["H"], std=c["std"], gate=c["gate"], seed=seed, dtype=dtype)
+# Seeded synthetic inputs live in gtr_b200/workloads.py (shared with the benchmark); re-exported for the tests.
+from gtr_b200.workloads import CONFIGS, config_inputs, make_inputs  # noqa: E402,F401
 
 
 def error_metrics(ref: torch.Tensor, got: torch.Tensor):
