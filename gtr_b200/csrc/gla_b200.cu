@@ -337,14 +337,10 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     if (gh < 0 || gw < 0 || static_cast<int64_t>(gh) * gw != a->T) return GLA_B200_ERR_SHAPE;
     if (a->direction >= 2 && (a->grid_h <= 0 || a->grid_w <= 0)) return GLA_B200_ERR_SHAPE;
     if (a->scale != a->scale || a->gk_normalizer < 0.f) return GLA_B200_ERR_ARG;
-#ifdef GLA_TRACE
-    const bool gated = false;             // debug builds carry the trace buffer in rms_weight
-#else
     const bool gated = a->out_gate != nullptr || a->rms_weight != nullptr;
     if (gated && (!a->out_gate || !a->rms_weight)) return GLA_B200_ERR_NULL;
     if (gated && (!aligned16(a->out_gate) || !aligned16(a->rms_weight))) return GLA_B200_ERR_ALIGN;
     if (gated && !(a->rms_eps >= 0.f)) return GLA_B200_ERR_ARG;
-#endif
     if (static_cast<int64_t>(a->B) * a->T * a->H == 0) {
         // nothing to compute; an empty sequence leaves the state as it came in
         const size_t state_bytes = static_cast<size_t>(a->B) * a->H * a->K * gla::kD * sizeof(float);
@@ -418,8 +414,9 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     P.NS = NS; P.cps = cps;
     P.num_items = nseq * NS;
     P.gated = gated ? 1 : 0;
-    if (a->scale > 0.f && a->scale < 3.0e38f) { P.q_exp = log2f(a->scale); P.q_mul = a->scale; P.o_mul = 1.f; }
-    else { P.q_exp = 0.f; P.q_mul = 1.f; P.o_mul = a->scale; }
+    // q and k each carry sqrt(scale) / 4 (head-room for the gate factors in fp16); the 16 comes back in the epilogue
+    if (a->scale > 0.f && a->scale < 3.0e38f) { P.q_exp = log2f(a->scale) - 4.f; P.q_mul = a->scale * 0.0625f; P.o_mul = 16.f; }
+    else { P.q_exp = -4.f; P.q_mul = 0.0625f; P.o_mul = a->scale * 16.f; }
     P.inv_norm = a->gk_normalizer > 0.f ? 1.f / a->gk_normalizer : 0.f;
     P.rms_eps = a->rms_eps;
     P.rms_w = gated ? static_cast<const __half*>(a->rms_weight) : nullptr;
@@ -430,8 +427,6 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
         if (rc != GLA_B200_OK) return rc;
         P.gate_sb = gs[0]; P.gate_st = gs[1]; P.gate_sh = gs[2];
     }
-    P.o = static_cast<__half*>(a->o);
-    P.o_sb = key.stride[gla::TO][0]; P.o_st = key.stride[gla::TO][1]; P.o_sh = key.stride[gla::TO][2];
     P.s0 = a->initial_state;
     P.sT = a->final_state;
     P.ctrl = reinterpret_cast<uint32_t*>(ws + L.ctrl);
@@ -440,8 +435,7 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     P.incl = reinterpret_cast<float*>(ws + L.incl);
     P.wait_limit_us = a->wait_limit ? a->wait_limit : 2000000u;
 #ifdef GLA_TRACE
-    P.trace = static_cast<unsigned long long*>(const_cast<void*>(a->rms_weight));
-    P.dbg = getenv("GLA_DBG") ? atoi(getenv("GLA_DBG")) : 0;   // debug builds smuggle the trace buffer here
+    P.trace = gla::g_trace_buffer;
 #endif
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
