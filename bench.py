@@ -378,6 +378,13 @@ def run_ours(args, rank, local_rank, world):
     import gtr_b200
     from oracle import gla_ref
 
+    if args.profile_backbone:
+        # a short run for a profiler: the backbone leg alone (three warm-up passes, graph capture, `--backbone-steps` replays)
+        out = run_backbone(args, rank, local_rank, world, dist)
+        if rank == 0:
+            print(json.dumps({"profile_backbone": out}))
+        return
+
     name = args.workload
     grid = workloads.CONFIGS[name]["grid"]
     host_sets, dev_sets, in_bytes = device_sets(name, dev, seed0=1000 * rank)
@@ -401,6 +408,17 @@ def run_ours(args, rank, local_rank, world):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.profile_forwards > 0:
+        # a short run for a profiler: the same forwards on the same inputs, no one-second warm-up, nothing else
+        for i in range(args.warmup + args.profile_forwards):
+            step(i)
+        torch.cuda.synchronize()
+        gtr_b200.check_status(ws)
+        if rank == 0:
+            print(json.dumps({"profile_forwards": args.profile_forwards, "warmup_forwards": args.warmup,
+                              "config": workload_config(args.workload, B, H, T, K)}))
+        return
 
     # ---- device-resident timing.  Warm-up: at least `warmup` steps and one second under load (clocks ramp);
     # the clock sampler then runs across the timed region only.
@@ -585,6 +603,10 @@ def main():
     ap.add_argument("--backbone-batch", type=int, default=32,
                     help="images per backbone step over all ranks (32 = the named configuration; smaller for profiling)")
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads, CPU baselines and comparator")
+    ap.add_argument("--profile-backbone", action="store_true",
+                    help="run only the backbone leg (--backbone-batch, --backbone-steps) and exit (for ncu)")
+    ap.add_argument("--profile-forwards", type=int, default=0,
+                    help="run only warmup + N forwards of the workload (for ncu) and exit")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     args = ap.parse_args()

@@ -37,6 +37,17 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
+// The forward kernel's instantiations: bit 2 fused epilogue, bit 1 raw-logit gates, bit 0 reversed scan.
+const void* fwd_kernel(int variant) {
+    using gla::gla_fwd_kernel;
+    static const void* const table[8] = {
+        reinterpret_cast<const void*>(&gla_fwd_kernel<false, false, false>), reinterpret_cast<const void*>(&gla_fwd_kernel<false, false, true>),
+        reinterpret_cast<const void*>(&gla_fwd_kernel<false, true, false>),  reinterpret_cast<const void*>(&gla_fwd_kernel<false, true, true>),
+        reinterpret_cast<const void*>(&gla_fwd_kernel<true, false, false>),  reinterpret_cast<const void*>(&gla_fwd_kernel<true, false, true>),
+        reinterpret_cast<const void*>(&gla_fwd_kernel<true, true, false>),   reinterpret_cast<const void*>(&gla_fwd_kernel<true, true, true>)};
+    return table[variant & 7];
+}
+
 struct DeviceInfo {
     bool ok = false;
     int sms = 0;
@@ -57,13 +68,14 @@ int device_info(int dev, DeviceInfo* out) {
             snprintf(g_cuda_err, sizeof(g_cuda_err), "device %d has compute capability %d.x, need 10.x", dev, major);
             return GLA_B200_ERR_DEVICE;
         }
-        e = cudaFuncSetAttribute(gla::gla_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gla::kSmemBytes);
+        for (int v = 0; v < 8 && e == cudaSuccess; ++v)
+            e = cudaFuncSetAttribute(fwd_kernel(v), cudaFuncAttributeMaxDynamicSharedMemorySize, gla::kSmemBytes);
         if (e != cudaSuccess) { note_cuda("cudaFuncSetAttribute", e); return GLA_B200_ERR_CUDA; }
         // The warpgroups of the kernel re-divide the registers the CTA was launched with (setmaxnreg); a group that
         // asks for more than the others release would wait for ever, so the budgets are checked against what this
         // build of the kernel really gets at launch.
         cudaFuncAttributes fa;
-        e = cudaFuncGetAttributes(&fa, gla::gla_fwd_kernel);
+        e = cudaFuncGetAttributes(&fa, fwd_kernel(0));
         if (e != cudaSuccess) { note_cuda("cudaFuncGetAttributes", e); return GLA_B200_ERR_CUDA; }
         if (fa.numRegs * gla::kThreads < gla::kRegBudgetTotal) {
             snprintf(g_cuda_err, sizeof(g_cuda_err), "kernel launches with %d registers per thread, its register budgets need %d",
@@ -442,7 +454,10 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     ce = cudaMemsetAsync(ws, 0, L.clear_bytes, stream);
     if (ce != cudaSuccess) { note_cuda("cudaMemsetAsync", ce); return GLA_B200_ERR_CUDA; }
     const int grid = P.num_items < slots ? P.num_items : slots;
-    gla::gla_fwd_kernel<<<grid, gla::kThreads, gla::kSmemBytes, stream>>>(maps, P);
+    const int variant = (P.gated ? 4 : 0) | (P.inv_norm > 0.f ? 2 : 0) | (P.rev ? 1 : 0);
+    void* kargs[2] = {const_cast<gla::Maps*>(&maps), &P};
+    ce = cudaLaunchKernel(fwd_kernel(variant), dim3(grid), dim3(gla::kThreads), kargs, gla::kSmemBytes, stream);
+    if (ce != cudaSuccess) { note_cuda("cudaLaunchKernel", ce); return GLA_B200_ERR_CUDA; }
     ce = cudaPeekAtLastError();
     if (ce != cudaSuccess) { note_cuda("kernel launch", ce); return GLA_B200_ERR_CUDA; }
     return GLA_B200_OK;

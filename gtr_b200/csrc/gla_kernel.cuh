@@ -53,6 +53,7 @@
 #include "gla_trace.cuh"      // development builds only: in-kernel timeline
 #else
 #define GLA_EV(id) do { } while (0)
+#define GLA_EVV(id, val) do { } while (0)
 #endif
 
 namespace gla {
@@ -74,6 +75,17 @@ constexpr int kTmemCols = 512;
 constexpr uint32_t kTmT = 0;              // per team: scores, then outputs of its chunk (64 columns each)
 constexpr uint32_t kTmX = 192;            // per team: gate sums relative to the chunk's reference
 constexpr uint32_t kTmInc = 384;          // state increments: two buffers of 64 columns
+#ifndef GLA_L2HINT
+#define GLA_L2HINT 1
+#endif
+#ifndef GLA_REVPRE
+#define GLA_REVPRE 1
+#endif
+constexpr bool kL2Hints = GLA_L2HINT != 0;
+// The pre-pass walks its segment from the last chunk to the first, so that the output pass, which starts at the first,
+// meets the tiles in the reverse of the order they were brought into L2: what a least-recently-used cache still holds
+// of the segment is what is asked for next.
+constexpr bool kBackwardPrePass = GLA_REVPRE != 0;
 constexpr int kSlots = 8;                 // per-chunk exchange slots (reference vector, exact-path flag): outlive the stage
 static_assert(kSlots >= kNumStages + 3 && (kSlots & (kSlots - 1)) == 0, "exchange slots must outlive the stage ring");
 constexpr float kLog2e = 1.4426950408889634f;
@@ -246,6 +258,20 @@ struct BoxWalker {
             f(id, row);
             row += R;
             len -= R;
+        }
+    }
+    // one chunk back along the scan
+    __device__ __forceinline__ void retreat(const Params& P) {
+        if (!P.rev) {
+            u_lo -= kChunk;
+            r -= kChunk;
+            while (r < 0) { r += P.Hc; --c; }
+        } else if (u_lo < 0) {
+            *this = BoxWalker(P, P.T - u_lo - 2 * kChunk);
+        } else {
+            u_lo += kChunk;
+            r += kChunk;
+            while (r >= P.Hc) { r -= P.Hc; ++c; }
         }
     }
     __device__ __forceinline__ void advance(const Params& P) {
@@ -421,13 +447,8 @@ __device__ __noinline__ void logits_to_log_gates(uint32_t tg, float inv_norm, bo
 // sides of the diagonal.
 __device__ __forceinline__ void mask_and_store_scores(bool rev, uint32_t a16, uint32_t rho, uint32_t j0, float* x) {
     const int lim = static_cast<int>(rho) - static_cast<int>(j0);
-    if (!rev) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) x[j] = (j <= lim) ? x[j] : 0.f;
-    } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) x[j] = (j >= lim) ? x[j] : 0.f;
-    }
+    for (int j = 0; j < 32; ++j) x[j] = (rev ? (j >= lim) : (j <= lim)) ? x[j] : 0.f;
     store_row_f16<4>(a16, rho, j0 >> 3, x);
 }
 
@@ -507,6 +528,9 @@ template <int N> __device__ __forceinline__ void reg_budget() {
     else if constexpr (N < kLaunchRegs) reg_dealloc<N>();
 }
 
+// One instantiation per combination of fused epilogue, raw-logit gates and scan sense: each holds only the code of its
+// own case, which keeps the instruction working set of the concurrently running roles small.
+template <bool kGated, bool kLogits, bool kRev>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params P) {
     extern __shared__ uint8_t smem_raw[];
@@ -520,6 +544,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
 #ifdef GLA_TRACE
     uint32_t trace_n = 0;
 #endif
+    GLA_EV(1);
+    GLA_EVV(2, globaltimer_ns());
     constexpr int kWarpTeam = kStateWarps;
     constexpr int kWarpProducer = kWarpTeam + kTeams * kTeamWarps, kWarpX = kWarpProducer + 1;
 
@@ -558,7 +584,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     //   pre-pass:    -1 where the source row is after the output row, 0 elsewhere                            (G - G_L)
     for (int e = tid; e < kChunk * kChunk; e += kThreads) {
         const uint32_t r = static_cast<uint32_t>(e) >> 6, s = static_cast<uint32_t>(e) & 63u;
-        const bool at_or_before = P.rev ? (s >= r) : (s <= r);
+        const bool at_or_before = kRev ? (s >= r) : (s <= r);
         const uint32_t o = sw_f16(r, s);
         *reinterpret_cast<__half*>(base_ptr + kOffLmat + o) = __float2half(at_or_before ? 0.5f : -0.5f);
         *reinterpret_cast<__half*>(base_ptr + kOffLmat + kTileBytes + o) = __float2half(at_or_before ? 0.f : -1.f);
@@ -574,9 +600,10 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    GLA_EV(5);
     const uint32_t tmem = __shfl_sync(0xffffffffu, M.tmem_base, 0);
-    const bool logits = P.inv_norm > 0.f;
-    const bool rev = P.rev != 0;
+    constexpr bool logits = kLogits;
+    constexpr bool rev = kRev;
     const float hk = 0.5f * P.q_exp, hq = P.q_exp - hk;       // k's and q's share of the output scale (log2)
 
     // Every role walks the same sequence of work items and chunks and keeps its own counters:
@@ -590,6 +617,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     auto next_item = [&]() -> int {
         if (tid == 0) M.item = static_cast<int>(atomicAdd(P.ctrl, 1u));
         __syncthreads();
+        GLA_EV(3);
+        GLA_EVV(6, M.item);
         return __shfl_sync(0xffffffffu, M.item, 0);   // known to be warp-uniform
     };
 
@@ -643,16 +672,18 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
 
             for (int pass = 0; pass < npass; ++pass) {
                 const bool state_only = it.state_pass && pass == 0;
+                const bool back = state_only && kBackwardPrePass;
                 if (state_only || it.seg == 0) {
                     // the pre-pass reduces the segment to (decay, increment) from a zero state; segment 0 starts
-                    // from the initial state in either pass
-                    if (it.seg == 0) load_initial();
+                    // from the initial state in either pass (a backward pre-pass adds it at the end)
+                    if (it.seg == 0 && !back) load_initial();
                     else {
 #pragma unroll
                         for (int x = 0; x < 32; ++x) S[x] = 0.f;
                     }
                 } else {
                     // decoupled look-back: S <- state entering this segment
+                    GLA_EV(60);
 #pragma unroll
                     for (int x = 0; x < 32; ++x) S[x] = 0.f;
                     float dlog = 0.f;
@@ -712,6 +743,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         if (tid == 0) st_release_gpu(P.flags + slot, 2u);
                     }
                 }
+                GLA_EV(61);
                 if (it.nchunks > 0) {
                     // the first chunk's reference is known once its gate math is done; every chunk's `ops_ready` phase
                     // is waited for exactly once by this group (here, or as "the next chunk" inside the loop)
@@ -739,7 +771,12 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     }
                     const float v = ld_shared_f(smem_u32(&M.vec[ctr & (kSlots - 1)][my_c]));
                     float ta, tb;
-                    if (state_only) { ta = v; tb = 0.f; gsum += v; }
+                    if (state_only) {
+                        // forward: S' = 2^G_L S + inc; backward: S' = S + 2^(decay of the chunks after this one) inc
+                        ta = back ? 0.f : v;
+                        tb = back ? gsum : 0.f;
+                        gsum += v;
+                    }
                     else {
                         const bool wide = M.wide[ctr & (kSlots - 1)] != 0u;
                         ta = wide ? 2.f * v - hk : v - hk;
@@ -773,7 +810,18 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     GLA_EV(15);
                 }
 
+                GLA_EV(62);
                 if (state_only) {
+                    if (back && it.seg == 0 && real_row && P.s0 != nullptr) {
+                        const float dtot = ex2(gsum);
+                        const float4* src = reinterpret_cast<const float4*>(P.s0 + srow);
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) {
+                            const float4 v4 = __ldg(src + x);
+                            S[4 * x] = fmaf(dtot, v4.x, S[4 * x]); S[4 * x + 1] = fmaf(dtot, v4.y, S[4 * x + 1]);
+                            S[4 * x + 2] = fmaf(dtot, v4.z, S[4 * x + 2]); S[4 * x + 3] = fmaf(dtot, v4.w, S[4 * x + 3]);
+                        }
+                    }
                     if (it.seg == 0) {
                         publish(P.incl + slot * (kD * kD) + hoff, 2u);
                     } else {
@@ -805,6 +853,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         constexpr uint32_t idO = umma_idesc(FMT_F16, 0, 1, 64, 64);     // A16 x v, qt x St
         const bool issuer = tw == 0;                  // the team's first warp issues its MMAs (one elected lane),
         const bool storer = tw == 1;                  // its second warp the output stores
+        const uint64_t pol_stream = l2_policy_stream();
         uint32_t oturn = 0;                           // output-pass chunks this team has taken: use count of a_done / o_done
         while (true) {
             const int item = next_item();
@@ -823,7 +872,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     mbar_wait(ctx, &M.full[s], (ctr / kNumStages) & 1u);
                     GLA_EV(12);
                     if (logits) {
-                        logits_to_log_gates(tg, P.inv_norm, rev, chunk_valid((it.first_chunk + i) * kChunk, P.T), tw, l);
+                        const int ci = it.first_chunk + ((state_only && kBackwardPrePass) ? it.nchunks - 1 - i : i);
+                        logits_to_log_gates(tg, P.inv_norm, rev, chunk_valid(ci * kChunk, P.T), tw, l);
                         warp_arrive(&M.g_ready[s], l);
                     }
                     // ---- gate sums of this thread's row and channel half
@@ -947,7 +997,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     // ---- scores: TMEM -> causal mask -> fp16 tile over the gate tile
                     // fused epilogue: this thread's half row of the chunk's output gate is asked for now, into L2
                     const uint4* gp = nullptr;
-                    if (P.gated) {
+                    if (kGated) {
                         const int p0 = (it.first_chunk + i) * kChunk;
                         const int u = (rev ? (P.T - p0 - kChunk) : p0) + static_cast<int>(rho);   // position along the scan
                         if (u >= 0 && u < P.T) {
@@ -998,7 +1048,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     tc_fence_after();
                     tmem_half_row(tmem, tw, kTmT + 64u * team, x);
                     tc_fence_before();
-                    if (!P.gated) {
+                    if (!kGated) {
                         if (P.o_mul != 1.f) {         // scale not folded into q and k (zero, negative or not finite)
 #pragma unroll
                             for (int e = 0; e < 32; ++e) x[e] *= P.o_mul;
@@ -1033,7 +1083,11 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     if (storer && elect_one()) {
                         const BoxWalker bw(P, (it.first_chunk + i) * kChunk);
                         bw.for_each(P, [&](int id, int r, int c, int row) {
-                            tma_store_5d(&maps.m[TO][id], out_tile + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
+                            if (kL2Hints)
+                                tma_store_5d_hint(&maps.m[TO][id], out_tile + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b,
+                                                  pol_stream);
+                            else
+                                tma_store_5d(&maps.m[TO][id], out_tile + static_cast<uint32_t>(row) * 128u, 0, it.h, r, c, it.b);
                         });
                         tma_store_commit();
                     }
@@ -1057,9 +1111,17 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
             const int npass = it.state_pass ? 2 : 1;
             if (w == kWarpProducer) {
                 // ------------------------------------------------------------ TMA producer
+                const uint64_t pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
                 for (int pass = 0; pass < npass; ++pass) {
                     const bool state_only = it.state_pass && pass == 0;
-                    BoxWalker bw(P, it.first_chunk * kChunk);
+                    const bool back = state_only && kBackwardPrePass;
+                    BoxWalker bw(P, (it.first_chunk + (back ? it.nchunks - 1 : 0)) * kChunk);
+                    // tiles of a pre-pass are read again by the output pass; everything else is read once
+                    const uint64_t pol = state_only ? pol_keep : pol_stream;
+                    auto load = [&](uint32_t dst, int tensor, int id, uint32_t bar, int r, int c) {
+                        if (kL2Hints) tma_load_5d_hint(dst, &maps.m[tensor][id], bar, 0, it.h, r, c, it.b, pol);
+                        else tma_load_5d(dst, &maps.m[tensor][id], bar, 0, it.h, r, c, it.b);
+                    };
                     for (int i = 0; i < it.nchunks; ++i, ++ctr) {
                         const uint32_t s = ctr % kNumStages, n = ctr / kNumStages;
                         mbar_wait(ctx, &M.empty[s], (n & 1u) ^ 1u);
@@ -1071,11 +1133,10 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             const uint32_t stage = base + kOffStage + s * kStageBytes;
                             bw.for_each(P, [&](int id, int r, int c, int row) {
                                 const uint32_t off = static_cast<uint32_t>(row) * 128u;
-                                tma_load_5d(stage + 2 * kTileBytes + off, &maps.m[TG][id], bar, 0, it.h, r, c, it.b);
-                                tma_load_5d(stage + 1 * kTileBytes + off, &maps.m[TK][id], bar, 0, it.h, r, c, it.b);
-                                if (!state_only)
-                                    tma_load_5d(stage + 0 * kTileBytes + off, &maps.m[TQ][id], bar, 0, it.h, r, c, it.b);
-                                tma_load_5d(stage + 3 * kTileBytes + off, &maps.m[TV][id], bar, 0, it.h, r, c, it.b);
+                                load(stage + 2 * kTileBytes + off, TG, id, bar, r, c);
+                                load(stage + 1 * kTileBytes + off, TK, id, bar, r, c);
+                                if (!state_only) load(stage + 0 * kTileBytes + off, TQ, id, bar, r, c);
+                                load(stage + 3 * kTileBytes + off, TV, id, bar, r, c);
                             });
                             // rows the sequence does not have: boxes whose row coordinate lies past the column's end
                             // read nothing and fill their part of the tile with zeros
@@ -1089,7 +1150,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             });
                         }
                         __syncwarp();
-                        bw.advance(P);
+                        if (back) bw.retreat(P);
+                        else bw.advance(P);
                     }
                 }
             } else if (w == kWarpX) {
@@ -1120,8 +1182,11 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         }
     }
 
+    GLA_EV(4);
     tc_fence_before();
     __syncthreads();
+    GLA_EV(7);
+    GLA_EVV(8, globaltimer_ns());
     if (w == kWarpProducer) tmem_dealloc(tmem, kTmemCols);
 }
 

@@ -24,12 +24,20 @@ __device__ __forceinline__ void dw_unpack8(const uint4& v, float* x) {
     }
 }
 
+// acc[0..7] += w[0..7] * y[0..7] with the fp16 operands taken as they are: fma.rn.f32.f16 multiplies two fp16 values
+// and accumulates in fp32 in one instruction (exact product, one rounding), so the taps cost no conversions.
+__device__ __forceinline__ void dw_fma2(float& a0, float& a1, uint32_t w, uint32_t y) {
+    asm("{\n\t.reg .b16 wl, wh, yl, yh;\n\t"
+        "mov.b32 {wl, wh}, %2;\n\tmov.b32 {yl, yh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, wl, yl, %0;\n\tfma.rn.f32.f16 %1, wh, yh, %1;\n\t}"
+        : "+f"(a0), "+f"(a1)
+        : "r"(w), "r"(y));
+}
 __device__ __forceinline__ void dw_fma8(float* acc, const uint4& wv, const uint4& yv) {
-    float w[8], y[8];
-    dw_unpack8(wv, w);
-    dw_unpack8(yv, y);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[i], y[i], acc[i]);
+    dw_fma2(acc[0], acc[1], wv.x, yv.x);
+    dw_fma2(acc[2], acc[3], wv.y, yv.y);
+    dw_fma2(acc[4], acc[5], wv.z, yv.z);
+    dw_fma2(acc[6], acc[7], wv.w, yv.w);
 }
 
 // gate, y, out: [B, hg, wg, C] fp16 contiguous; wt: [3][3][C] fp16 (tap-major); bias: [C] fp16 or null.
@@ -44,7 +52,10 @@ __device__ __forceinline__ void dw_fma8(float* acc, const uint4& wv, const uint4
 #ifndef DW_MINB
 #define DW_MINB 4
 #endif
-constexpr int kDwTileR = DW_TR, kDwTileC = 16, kDwSlab = 16;
+#ifndef DW_TC
+#define DW_TC 16
+#endif
+constexpr int kDwTileR = DW_TR, kDwTileC = DW_TC, kDwSlab = 16;
 constexpr int kDwTileThreads = kDwTileR * kDwSlab;                                   // 128
 constexpr int kDwTilePos = (kDwTileR + 2) * (kDwTileC + 2);                          // 180 positions
 constexpr int kDwTileSmem = kDwTilePos * kDwSlab * 16;                               // 46,080 bytes
@@ -71,6 +82,19 @@ __global__ void __launch_bounds__(kDwTileThreads, DW_MINB) swiglu_dwconv_kernel(
     const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(dw_smem));
     const uint4* y4 = reinterpret_cast<const uint4*>(y);
     const long long img = static_cast<long long>(b) * hg * wg;
+
+    // ---- the gate vectors this thread will need (one tile row, 16 columns) are asked into L2 first: they are read
+    // straight from global memory during the compute phase, two columns ahead of their use, which covers an L2 hit
+    // but not a DRAM access under load.  One request per 128-byte line.
+    {
+        const int pci = tid % kDwSlab, prow = r0 + tid / kDwSlab, pcg = cg0 + pci;
+        if ((pci & 7) == 0 && prow < hg && pcg < CG) {
+            const uint4* gp = reinterpret_cast<const uint4*>(gate) + (img + static_cast<long long>(prow) * wg + c0) * CG + pcg;
+            const int n = min(kDwTileC, wg - c0);
+            for (int j = 0; j < n; ++j)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(gp + static_cast<long long>(j) * CG) : "memory");
+        }
+    }
 
     // ---- fill: position (pr, pc) of the halo tile is grid cell (r0 - 1 + pr, c0 - 1 + pc); zeros outside the grid
     for (int idx = tid; idx < kDwTilePos * kDwSlab; idx += kDwTileThreads) {
@@ -113,39 +137,47 @@ __global__ void __launch_bounds__(kDwTileThreads, DW_MINB) swiglu_dwconv_kernel(
     const uint4* g4 = reinterpret_cast<const uint4*>(gate);
     uint4* o4 = reinterpret_cast<uint4*>(out);
     const int ncol = min(kDwTileC, wg - c0);
-    uint4 l0 = ld(trow, 0), l1 = ld(trow + 1, 0), l2 = ld(trow + 2, 0);
-    uint4 m0 = ld(trow, 1), m1 = ld(trow + 1, 1), m2 = ld(trow + 2, 1);
-    // the gate vectors come straight from global memory, asked for two columns ahead of their use
+    // the 3x3 window slides along the row: three columns of three 16-byte vectors in registers; the column loop is
+    // unrolled so that the columns change roles by renaming, not by moves
+    uint4 win[3][3];                     // win[column slot][row]
+#pragma unroll
+    for (int rr = 0; rr < 3; ++rr) { win[0][rr] = ld(trow + rr, 0); win[1][rr] = ld(trow + rr, 1); }
+    // the gate vectors come straight from global memory (L2 after the prefetch above), two columns ahead of their use
     const long long pcol = base + static_cast<long long>(c0) * CG;
-    uint4 ga = __ldg(g4 + pcol), gb = ncol > 1 ? __ldg(g4 + pcol + CG) : ga;
-#pragma unroll 1
-    for (int j = 0; j < ncol; ++j) {
-        const uint4 n0 = ld(trow, j + 2), n1 = ld(trow + 1, j + 2), n2 = ld(trow + 2, j + 2);
-        const long long p = pcol + static_cast<long long>(j) * CG;
-        const uint4 gv = ga;
-        ga = gb;
-        if (j + 2 < ncol) gb = __ldg(g4 + p + 2 * static_cast<long long>(CG));
-        float acc[8];
+    uint4 gq[3];
+    gq[0] = __ldg(g4 + pcol);
+    gq[1] = ncol > 1 ? __ldg(g4 + pcol + CG) : gq[0];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = bv[i];
-        dw_fma8(acc, wv[0], l0); dw_fma8(acc, wv[1], m0); dw_fma8(acc, wv[2], n0);
-        dw_fma8(acc, wv[3], l1); dw_fma8(acc, wv[4], m1); dw_fma8(acc, wv[5], n1);
-        dw_fma8(acc, wv[6], l2); dw_fma8(acc, wv[7], m2); dw_fma8(acc, wv[8], n2);
-        float g[8];
-        dw_unpack8(gv, g);
-        uint4 o;
-        __half2* oh = reinterpret_cast<__half2*>(&o);
+    for (int j = 0; j < kDwTileC; ++j) {
+        if (j < ncol) {
+            const int sl = j % 3, sm = (j + 1) % 3, sn = (j + 2) % 3;     // left, middle, new column slots
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float h0 = 0.5f * g[2 * i], h1 = 0.5f * g[2 * i + 1];      // silu(x) = h + h * tanh(h), h = x / 2
-            float t0, t1;
-            asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(h0));
-            asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(h1));
-            oh[i] = __floats2half2_rn(fmaf(h0, t0, h0) * acc[2 * i], fmaf(h1, t1, h1) * acc[2 * i + 1]);
+            for (int rr = 0; rr < 3; ++rr) win[sn][rr] = ld(trow + rr, j + 2);
+            const long long p = pcol + static_cast<long long>(j) * CG;
+            if (j + 2 < ncol) gq[(j + 2) % 3] = __ldg(g4 + p + 2 * static_cast<long long>(CG));
+            float acc[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = bv[i];
+#pragma unroll
+            for (int rr = 0; rr < 3; ++rr) {
+                dw_fma8(acc, wv[3 * rr + 0], win[sl][rr]);
+                dw_fma8(acc, wv[3 * rr + 1], win[sm][rr]);
+                dw_fma8(acc, wv[3 * rr + 2], win[sn][rr]);
+            }
+            float g[8];
+            dw_unpack8(gq[j % 3], g);
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float h0 = 0.5f * g[2 * i], h1 = 0.5f * g[2 * i + 1];      // silu(x) = h + h * tanh(h), h = x / 2
+                float t0, t1;
+                asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(h0));
+                asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(h1));
+                oh[i] = __floats2half2_rn(fmaf(h0, t0, h0) * acc[2 * i], fmaf(h1, t1, h1) * acc[2 * i + 1]);
+            }
+            o4[p] = o;
         }
-        o4[p] = o;
-        l0 = m0; l1 = m1; l2 = m2;
-        m0 = n0; m1 = n1; m2 = n2;
     }
 }
 
