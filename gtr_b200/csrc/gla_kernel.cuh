@@ -6,8 +6,9 @@
 // predecessors are always held by CTAs that already run.  For every segment but the last
 // of a sequence the CTA first streams k, g, v only and reduces the segment to an aggregate
 // (decay, state increment), publishes it, obtains its incoming state from its predecessors
-// by a decoupled look-back, and then streams q, k, g, v once more (k, g, v come from L2) to
-// produce the outputs.  Replaces chunk_compute_S_kernel / chunk_scan_*_kernel /
+// by a decoupled look-back, and then streams q, k, g, v once more to produce the outputs (the
+// pre-pass walks the segment backwards and its copies carry an evict-last L2 priority, so that
+// k, g, v are still in L2 then).  Replaces chunk_compute_S_kernel / chunk_scan_*_kernel /
 // chunk_fwd_o_kernel of the reference (engine/gtr/backbone/csrc/gla_chunk.cuh:718-1394).
 //
 // Per chunk, with G the inclusive within-chunk cumulative log gate, G_L its value at the last
@@ -29,9 +30,9 @@
 // The state-only pre-pass uses X = G - G_L (a second constant matrix), whose exponents are never positive.
 //
 // Who does what.  Three teams of four warps take the chunks in turn; a team does everything of its chunk that
-// is elementwise -- gate factors, score mask, output epilogue -- and one elected thread of it issues the chunk's
-// MMAs and its output TMA store between those steps, so a chunk is handed from warp to warp only through the
-// tensor core.  While a team waits for an MMA the other two work.  A fourth group carries the state; one
+// is elementwise -- gate factors, score mask, output epilogue -- and elected threads of it issue the chunk's
+// MMAs (first warp) and its output TMA store (second warp) between those steps, so a chunk is handed from warp to
+// warp only through the tensor core.  While a team waits for an MMA the other two work.  A fourth group carries the state; one
 // service warp loads the tiles, another issues the gate-sum MMAs as soon as a chunk's tiles have landed.
 //
 // Tensor memory (512 columns): per team one 64-column accumulator that holds, one after the other, the scores and
@@ -54,6 +55,7 @@
 #else
 #define GLA_EV(id) do { } while (0)
 #define GLA_EVV(id, val) do { } while (0)
+#define GLA_TRACE_PICK(item) do { } while (0)
 #endif
 
 namespace gla {
@@ -543,6 +545,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     const int w = tid >> 5, l = tid & 31;
 #ifdef GLA_TRACE
     uint32_t trace_n = 0;
+    int trace_slot = -2;
+    const long long trace_t0 = clock64();
 #endif
     GLA_EV(1);
     GLA_EVV(2, globaltimer_ns());
@@ -617,6 +621,8 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
     auto next_item = [&]() -> int {
         if (tid == 0) M.item = static_cast<int>(atomicAdd(P.ctrl, 1u));
         __syncthreads();
+        GLA_TRACE_PICK(M.item);
+        GLA_EVV(9, trace_t0);
         GLA_EV(3);
         GLA_EVV(6, M.item);
         return __shfl_sync(0xffffffffu, M.item, 0);   // known to be warp-uniform
