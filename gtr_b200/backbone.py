@@ -48,6 +48,10 @@ def oriented_dwconv_weight(w: torch.Tensor, direction: int) -> torch.Tensor:
     return w.contiguous()
 
 
+# (B, T, heads, device) -> (operator workspace, operator output), shared by every attention module of the process
+_GLA_BUFFERS: dict = {}
+
+
 class GatedLinearAttention(nn.Module):
     def __init__(self, hidden_size: int, num_heads: int, expand_k: float = 1.0, expand_v: float = 1.0,
                  gate_low_rank_dim: int = 16, gate_logit_normalizer: float = 16.0, norm_eps: float = 1e-5):
@@ -73,11 +77,16 @@ class GatedLinearAttention(nn.Module):
 
     def _gla_buffers(self, B: int, T: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
         """Workspace and output are kept per shape so that captured graphs see stable pointers
-        (reference: _get_or_make_gla_ws, vit_adapter.py:420-433)."""
-        key = (B, T, device)
+        (reference: _get_or_make_gla_ws, vit_adapter.py:420-433).  All attention modules of a process share one pair
+        per (B, T, heads, device): the blocks run back to back on one stream, the operator clears its control words
+        at the start of every call and a block's output is consumed by its o_proj before the next block's operator
+        runs, so twelve blocks need one worst-case workspace (hundreds of MB at the backbone's shape), not twelve."""
+        key = (B, T, self.num_heads, str(device))
         if self._ws_key != key:
-            self._ws = ops.make_workspace(B, T, self.num_heads, device)
-            self._out = torch.empty(B, T, self.num_heads, HEAD_DIM, dtype=torch.float16, device=device)
+            if key not in _GLA_BUFFERS:
+                _GLA_BUFFERS[key] = (ops.make_workspace(B, T, self.num_heads, device),
+                                     torch.empty(B, T, self.num_heads, HEAD_DIM, dtype=torch.float16, device=device))
+            self._ws, self._out = _GLA_BUFFERS[key]
             self._ws_key = key
         return self._ws, self._out
 
