@@ -303,25 +303,10 @@ __device__ __forceinline__ float lg2(float x) {   // log2(x), one MUFU op
 }
 // log(sigmoid(x)) = min(x, 0) - log(1 + exp(-|x|)), with the two MUFU ops ex2 and lg2; absolute error
 // below 1e-6, far inside the fp16 grid the result is rounded to
-// logsigmoid(x) = min(x, 0) - log1p(e^-|x|).  log1p(t) = t q(t) on (0, 1] with q a degree-5 fit (relative error below
-// 1e-5, far under the fp16 rounding the result gets): one special-function operation per value instead of two, the
-// rest on the FMA pipe -- the conversion of a chunk's raw-logit gates otherwise doubles the kernel's load on that pipe.
 __device__ __forceinline__ float logsigmoid_f(float x) {
-#if defined(GLA_LOGSIGMOID_LG2)
     const float t = ex2(-fabsf(x) * 1.4426950408889634f);
     return fminf(x, 0.f) - 0.6931471805599453f * lg2(1.f + t);
-#else
-    const float t = ex2(-fabsf(x) * 1.4426950408889634f);
-    float q = -0.02397957257926464f;
-    q = fmaf(q, t, 0.10150004923343658f);
-    q = fmaf(q, t, -0.2102936953306198f);
-    q = fmaf(q, t, 0.3252951502799988f);
-    q = fmaf(q, t, -0.49937260150909424f);
-    q = fmaf(q, t, 0.9999918341636658f);
-    return fmaf(-t, q, fminf(x, 0.f));
-#endif
 }
-// x * sigmoid(x) = h + h * tanh(h) with h = x / 2: one MUFU op (tanh.approx, relative error about 2^-11)
 __device__ __forceinline__ float silu_f(float x) {
     const float h = 0.5f * x;
     float t;
