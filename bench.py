@@ -530,6 +530,20 @@ def run_ours(args, rank, local_rank, world):
             backbone = run_backbone(args, rank, local_rank, world, dist)
         except Exception as e:   # reported, never hidden: the operator line below stays valid
             backbone = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    loader = None
+    if rank == 0 and not args.no_extras:
+        # what the kernel's loading scheme alone streams on this GPU (reads only, nothing computed): the ceiling the
+        # ring of five 32 KB stages per SM puts under any kernel built on it
+        try:
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            p4 = gtr_b200.stream_probe(ctas=min(144, sms), tiles=4, chunks=33, device=dev)
+            p3 = gtr_b200.stream_probe(ctas=min(96, sms), tiles=3, chunks=34, device=dev)
+            loader = {"what": "TMA ring of 5 stages x 64-row x 128-byte tiles per CTA, one head per CTA, cold L2, nothing computed; "
+                              "GB/s over the whole launch (start-up and tail included)",
+                      "output_pass_like": {"ctas": p4["ctas"], "tiles_per_chunk": 4, "GBs": p4["GBs"], "us": p4["us"]},
+                      "pre_pass_like": {"ctas": p3["ctas"], "tiles_per_chunk": 3, "GBs": p3["GBs"], "us": p3["us"]}}
+        except Exception as e:      # reported, never hidden
+            loader = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
     if rank == 0:
         # ---- sanity: the timed output equals the oracle on a slice (cheap, outside the timed region)
         from oracle import c_oracle
@@ -578,7 +592,7 @@ def run_ours(args, rank, local_rank, world):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo_bytes,
                          "kernel_us": kern_us, "kernel_us_stats": percentiles(per_fwd_us),
-                         "traffic": ncu_traffic_bytes(name)},
+                         "traffic": ncu_traffic_bytes(name), "loader_ceiling": loader},
             "cpu_baseline": None if cpu is None else {
                 "value": cpu[0], "unit": "tokens/s", "cores": cpu[3], "kind": "port",
                 "sample": f"first {cpu[4][1]} of {T} tokens of every sequence (B{cpu[4][0]} H{H}), fp32 PyTorch token "

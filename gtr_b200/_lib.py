@@ -39,6 +39,7 @@ EXPORTS = (
     "gla_b200_forward", "gla_b200_workspace_bytes", "gla_b200_check_status", "gla_b200_rmsnorm_gated",
     "gla_b200_trt_enqueue", "gla_b200_strerror", "gla_b200_last_cuda_error", "gla_b200_version",
     "gla_b200_forward_static", "gla_b200_selftest_wait_timeout", "gla_b200_swiglu_dwconv", "gla_b200_layernorm",
+    "gla_b200_stream_probe",
 )
 
 _lib = None
@@ -65,6 +66,8 @@ def lib() -> ctypes.CDLL:
     L.gla_b200_forward_static.restype = ctypes.c_int
     L.gla_b200_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint32, ctypes.c_void_p]
     L.gla_b200_selftest_wait_timeout.restype = ctypes.c_int
+    L.gla_b200_stream_probe.argtypes = [ctypes.c_void_p, ctypes.c_int64] + [ctypes.c_int32] * 4 + [ctypes.c_void_p] * 2
+    L.gla_b200_stream_probe.restype = ctypes.c_int
     L.gla_b200_workspace_bytes.argtypes = [ctypes.c_int32] * 5
     L.gla_b200_workspace_bytes.restype = ctypes.c_size_t
     L.gla_b200_check_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]

@@ -265,6 +265,48 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __half* x, con
     if (live) *(reinterpret_cast<uint4*>(y + row * 64) + sub) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+
+// ---- streaming probe: the loading scheme of the forward kernel with nothing behind it ---------------------
+constexpr int kProbeStages = 5, kProbeThreads = 64;
+__device__ __forceinline__ bool probe_wait(uint32_t bar, uint32_t parity) {
+    for (int n = 0; n < (1 << 22); ++n)
+        if (gla::mbar_try_wait(bar, parity)) return true;
+    return false;                                    // bounded: give up and say so
+}
+__global__ void __launch_bounds__(kProbeThreads) stream_probe_kernel(const __grid_constant__ CUtensorMap map, int heads, int tiles,
+                                                                     int chunks, int slab_rows, int* status) {
+    extern __shared__ uint8_t probe_smem[];
+    const uint32_t sb = (gla::smem_u32(probe_smem) + 1023u) & ~1023u;
+    __shared__ uint64_t full[kProbeStages], empty[kProbeStages];
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        for (int s = 0; s < kProbeStages; ++s) { gla::mbar_init(gla::smem_u32(&full[s]), 1); gla::mbar_init(gla::smem_u32(&empty[s]), 1); }
+        gla::fence_mbar_init();
+    }
+    __syncthreads();
+    const int head = blockIdx.x % heads, region = blockIdx.x / heads;
+    if (tid == 32) {                                 // consumer: hands every stage back as soon as it has landed
+        for (int i = 0; i < chunks; ++i) {
+            const int s = i % kProbeStages;
+            if (!probe_wait(gla::smem_u32(&full[s]), (i / kProbeStages) & 1)) { if (status) atomicExch(status, 1); break; }
+            gla::mbar_arrive(gla::smem_u32(&empty[s]));
+        }
+    } else if (tid == 0) {                           // producer
+        for (int i = 0; i < chunks; ++i) {
+            const int s = i % kProbeStages;
+            if (i >= kProbeStages && !probe_wait(gla::smem_u32(&empty[s]), ((i / kProbeStages) & 1) ^ 1)) { if (status) atomicExch(status, 2); break; }
+            const uint32_t bar = gla::smem_u32(&full[s]);
+            gla::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(tiles) * gla::kTileBytes);
+            const int row = (region * chunks + i) * gla::kChunk;
+            for (int t = 0; t < tiles; ++t)
+                asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                             ::"r"(sb + static_cast<uint32_t>(s * 4 + t) * gla::kTileBytes), "l"(reinterpret_cast<uint64_t>(&map)), "r"(bar),
+                               "r"(0), "r"(head), "r"(t * slab_rows + row) : "memory");
+        }
+    }
+    __syncthreads();
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------
@@ -460,6 +502,48 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     if (ce != cudaSuccess) { note_cuda("cudaLaunchKernel", ce); return GLA_B200_ERR_CUDA; }
     ce = cudaPeekAtLastError();
     if (ce != cudaSuccess) { note_cuda("kernel launch", ce); return GLA_B200_ERR_CUDA; }
+    return GLA_B200_OK;
+}
+
+int gla_b200_stream_probe(const void* buf, int64_t rows, int32_t heads, int32_t ctas, int32_t tiles, int32_t chunks,
+                          int32_t* status, void* stream_v) {
+    if (!buf) return GLA_B200_ERR_NULL;
+    if (heads <= 0 || ctas <= 0 || tiles < 1 || tiles > 4 || chunks <= 0 || rows <= 0) return GLA_B200_ERR_ARG;
+    if (!aligned16(buf)) return GLA_B200_ERR_ALIGN;
+    const int64_t slab_rows = rows / tiles;
+    const int64_t regions = (ctas + heads - 1) / heads;
+    if (regions * chunks * gla::kChunk > slab_rows || slab_rows * tiles > 0x7fffffffLL) return GLA_B200_ERR_ARG;
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) { note_cuda("cudaGetDevice", ce); return GLA_B200_ERR_CUDA; }
+    DeviceInfo di;
+    int rc = device_info(dev, &di);
+    if (rc != GLA_B200_OK) return rc;
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return GLA_B200_ERR_DEVICE;
+    CUtensorMap map;
+    const cuuint64_t gdim[3] = {static_cast<cuuint64_t>(gla::kD), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t gstr[2] = {static_cast<cuuint64_t>(gla::kD) * 2, static_cast<cuuint64_t>(heads) * gla::kD * 2};
+    const cuuint32_t box[3] = {static_cast<cuuint32_t>(gla::kD), 1, static_cast<cuuint32_t>(gla::kChunk)}, estr[3] = {1, 1, 1};
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(buf), gdim, gstr, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { note_cu("cuTensorMapEncodeTiled", static_cast<int>(r)); return GLA_B200_ERR_CUDA; }
+    const int smem = kProbeStages * gla::kStageBytes + 1024;
+    static std::mutex mu;
+    static bool attr[64] = {false};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev >= 0 && dev < 64 && !attr[dev]) {
+            ce = cudaFuncSetAttribute(stream_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (ce != cudaSuccess) { note_cuda("cudaFuncSetAttribute", ce); return GLA_B200_ERR_CUDA; }
+            attr[dev] = true;
+        }
+    }
+    stream_probe_kernel<<<ctas, kProbeThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(
+        map, heads, tiles, chunks, static_cast<int>(slab_rows), status);
+    ce = cudaPeekAtLastError();
+    if (ce != cudaSuccess) { note_cuda("stream probe launch", ce); return GLA_B200_ERR_CUDA; }
     return GLA_B200_OK;
 }
 

@@ -171,6 +171,39 @@ def check_status(ws: torch.Tensor) -> None:
         _lib.check(_lib.lib().gla_b200_check_status(ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(stream)))
 
 
+def stream_probe(ctas: int = 144, tiles: int = 4, chunks: int = 33, heads: int = 12, repeats: int = 5, device="cuda"):
+    """What the forward kernel's loading scheme alone streams on this GPU: `ctas` CTAs, each filling a ring of five
+    stages of `tiles` 64-row x 128-byte tiles by TMA from a [rows, heads, 64] fp16 tensor (one head per CTA, rows
+    strided by heads * 128 B as in the operator's inputs) and handing every stage back as soon as it has landed.
+    The L2 is flushed before every repeat.  Returns GB/s (best repeat, CUDA events around the launch, so start-up
+    and tail are included, as they are in the operator's own timing) and microseconds."""
+    dev = torch.device(device)
+    with torch.cuda.device(dev):
+        regions = -(-ctas // heads)
+        rows = tiles * (regions + 1) * chunks * 64
+        buf = torch.zeros(rows, heads, 64, dtype=torch.float16, device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        best = None
+        for r in range(repeats + 1):
+            flush.fill_(r)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _lib.check(_lib.lib().gla_b200_stream_probe(ctypes.c_void_p(buf.data_ptr()), rows, heads, ctas, tiles, chunks,
+                                                        ctypes.c_void_p(status.data_ptr()), ctypes.c_void_p(stream)))
+            e1.record()
+            torch.cuda.synchronize(dev)
+            us = e0.elapsed_time(e1) * 1e3
+            if r > 0 and (best is None or us < best):
+                best = us
+        if int(status.item()) != 0:
+            raise RuntimeError("gla_b200_stream_probe: a bounded wait gave up")
+        nbytes = ctas * chunks * tiles * 8192
+        return {"GBs": nbytes / best / 1e3, "us": best, "bytes": nbytes, "ctas": ctas, "tiles_per_chunk": tiles,
+                "chunks_per_cta": chunks, "stages": 5}
+
+
 def rmsnorm_gated(x, g, w, y, eps: float) -> None:
     """y <- x * rsqrt(mean(x^2) + eps) * w * silu(g), rows of 64.  Reference: ext.rmsnorm_gated
     (gla_torch_ext.cu:228-261; kernel gla_norm_gate.cuh:13-75).  y may alias x."""

@@ -124,6 +124,17 @@ int gla_b200_check_status(const void* workspace, void* stream);
  * No counterpart in the reference, whose device-side waits are unbounded. */
 int gla_b200_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint32_t limit_us, void* stream);
 
+/* Diagnostic: what the kernel's way of loading -- a ring of five stages of 64-row x 128-byte tiles per CTA, filled by
+ * TMA from a [rows, heads, 64] fp16 tensor with one head per CTA -- can stream on this GPU when nothing is computed.
+ * `ctas` CTAs (one per SM) each read `chunks` chunks of `tiles` tiles (3 = the pre-pass's k, g, v; 4 = the output
+ * pass's q, k, g, v) from their own rows of `buf`; the stage is handed back as soon as it has landed.  The caller times
+ * the call with events: bytes = ctas * chunks * tiles * 8192.  `status` (device, one int, may be NULL) is set to a
+ * non-zero value if a bounded wait gave up.  `buf` needs rows >= tiles * (ctas / heads + 1) * chunks * 64.
+ * bench.py reports the figure beside the roofline as the ceiling of the loading scheme itself; the reference has no
+ * counterpart. */
+int gla_b200_stream_probe(const void* buf, int64_t rows, int32_t heads, int32_t ctas, int32_t tiles, int32_t chunks,
+                          int32_t* status, void* stream);
+
 /* Replaces rmsnorm_gated (gla_torch_ext.cu:156-196, kernel gla_norm_gate.cuh:13-75):
  * y = x * rsqrt(mean(x^2) + eps) * w * silu(g) over rows of D = 64 fp16 values; y may alias x. */
 int gla_b200_rmsnorm_gated(const void* x, const void* g, const void* w, void* y,

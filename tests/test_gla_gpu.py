@@ -531,3 +531,11 @@ def test_k32_released_model_call(G):
     G.check_status(ws)
     m = gla_ref.error_metrics(y_ref, y.float().cpu())
     assert m["finite"] and m["rel_l2"] <= 1.5e-3, m
+
+
+def test_stream_probe_reports_a_plausible_rate(G):
+    """The loader-only diagnostic runs, none of its bounded waits gives up, and the rate is that of a B200's memory."""
+    for ctas, tiles in ((144, 4), (96, 3)):
+        r = G.stream_probe(ctas=ctas, tiles=tiles, chunks=33)
+        assert r["bytes"] == ctas * 33 * tiles * 8192
+        assert 500.0 < r["GBs"] < 9000.0, r
