@@ -374,9 +374,9 @@ def run_ours(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # stdout carries the one JSON line: keep NCCL's version banner (NCCL_DEBUG=VERSION on some boxes) off it
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # stdout carries the one JSON line: NCCL's own messages (the version banner at NCCL_DEBUG=VERSION or above,
+        # which some boxes set) go to stderr instead
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     import gtr_b200
     from oracle import gla_ref
