@@ -374,10 +374,19 @@ def run_ours(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # stdout carries the one JSON line: NCCL's own messages (the version banner at NCCL_DEBUG=VERSION or above,
-        # which some boxes set) go to stderr instead
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=dev)
+        # stdout carries the one JSON line.  NCCL prints its version banner straight to stdout when it first comes up
+        # (NCCL_DEBUG=VERSION is set on some boxes), so the descriptor points at stderr while it does.
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
     import gtr_b200
     from oracle import gla_ref
 
