@@ -539,3 +539,23 @@ def test_stream_probe_reports_a_plausible_rate(G):
         r = G.stream_probe(ctas=ctas, tiles=tiles, chunks=33)
         assert r["bytes"] == ctas * 33 * tiles * 8192
         assert 500.0 < r["GBs"] < 9000.0, r
+
+
+@pytest.mark.parametrize("B,H,T,direction,grid", [
+    (1, 1, 16384, 0, None),          # one long sequence: many segments, a look-back over many aggregates
+    (1, 2, 12000, 3, (100, 120)),    # the same on a reversed column scan with a ragged last chunk
+    (40, 8, 100, 1, None),           # more sequences than SMs, two chunks each: several work items per CTA
+    (25, 4, 2000, 2, (40, 50)),      # segmented sequences and several work items per CTA (pre-pass and output pass each)
+    (3, 5, 1000, 0, None),           # odd counts
+])
+def test_work_decompositions(G, B, H, T, direction, grid):
+    """Shapes that drive the work decomposition to its corners, with incoming and outgoing states."""
+    from oracle import c_oracle, gla_ref
+    q, k, v, g = gla_ref.make_inputs(B, T, H, seed=B + T)
+    s0 = torch.randn(B, H, 64, 64, generator=torch.Generator().manual_seed(T)) * 0.5
+    ref, ref_s = c_oracle.forward(q, k, v, g, direction=direction, grid_hw=grid, initial_state=s0,
+                                  output_final_state=True)
+    got, got_s = _run(G, q, k, v, g, direction=direction, grid_hw=grid, s0=s0, final=True)
+    _check(ref, got, relative_abs=True)
+    assert torch.isfinite(got_s).all()
+    assert ((got_s - ref_s).norm() / ref_s.norm()).item() < 5e-4
