@@ -150,18 +150,47 @@ def chunk_gla_with_ws(q, k, v, gk, scale, ws, **kw) -> torch.Tensor:
 def chunk_gla(q, k, v, g, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,
               output_final_state: bool = False, cu_seqlens=None, *, direction=0, grid_hw=None,
               gk_normalizer: float = 0.0, segments: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-    """FLA-style call: returns (o, final_state).  Allocates output, workspace and final state."""
-    if cu_seqlens is not None:
-        raise NotImplementedError("variable-length batches (cu_seqlens) are not part of this operator")
+    """FLA-style call: returns (o, final_state).  Allocates output, workspace and final state.
+
+    `cu_seqlens` (the FLA convention the reference block passes through, vit_adapter.py:448-451,566-568): a batch of
+    one row holding N sequences back to back, `cu_seqlens` their N + 1 cumulative offsets.  Every sequence is one
+    launch on its slice of the row (the operator takes strided views, so nothing is copied); states are [N, H, K, 64]."""
     B, T, H, K = q.shape
     if scale is None:
         scale = K ** -0.5
-    ws = make_workspace(B, T, H, q.device)
     o = torch.empty(B, T, H, kV, dtype=torch.float16, device=q.device)
+    if cu_seqlens is not None:
+        if B != 1:
+            raise ValueError("cu_seqlens needs a batch of one row, as in FLA")
+        if direction != 0 or grid_hw is not None:
+            raise ValueError("cu_seqlens describes plain forward scans")
+        offs = [int(x) for x in (cu_seqlens.tolist() if hasattr(cu_seqlens, "tolist") else cu_seqlens)]
+        if len(offs) < 2 or offs[0] != 0 or offs[-1] != T or any(b < a for a, b in zip(offs, offs[1:])):
+            raise ValueError("cu_seqlens must rise from 0 to the row's length")
+        n = len(offs) - 1
+        if initial_state is not None and initial_state.shape[0] != n:
+            raise ValueError("initial_state needs one state per sequence")
+        final = torch.empty(n, H, K, kV, dtype=torch.float32, device=q.device) if output_final_state else None
+        ws = make_workspace(1, max(b - a for a, b in zip(offs, offs[1:])), H, q.device)
+        for i, (a, b) in enumerate(zip(offs, offs[1:])):
+            chunk_gla_run(q[:, a:b], k[:, a:b], v[:, a:b], g[:, a:b], scale, ws, o[:, a:b], gk_normalizer,
+                          initial_state=None if initial_state is None else initial_state[i:i + 1],
+                          final_state=None if final is None else final[i:i + 1], segments=segments)
+        return o, final
+    ws = make_workspace(B, T, H, q.device)
     final = torch.empty(B, H, K, kV, dtype=torch.float32, device=q.device) if output_final_state else None
     chunk_gla_run(q, k, v, g, scale, ws, o, gk_normalizer, direction=direction, grid_hw=grid_hw,
                   initial_state=initial_state, final_state=final, segments=segments)
     return o, final
+
+
+def fused_recurrent_gla(q, k, v, gk, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,
+                        output_final_state: bool = False, cu_seqlens=None):
+    """The call the reference block makes for sequences of at most 64 tokens and for decoding with a cached state
+    (FLA's fused_recurrent_gla, vit_adapter.py:441,560-562).  The chunkwise kernel serves any length from one token
+    up -- a short sequence is one ragged chunk -- and carries the state in fp32 from call to call, so this is the same
+    operator under the name the block expects."""
+    return chunk_gla(q, k, v, gk, scale, initial_state, output_final_state, cu_seqlens)
 
 
 def check_status(ws: torch.Tensor) -> None:

@@ -559,3 +559,45 @@ def test_work_decompositions(G, B, H, T, direction, grid):
     _check(ref, got, relative_abs=True)
     assert torch.isfinite(got_s).all()
     assert ((got_s - ref_s).norm() / ref_s.norm()).item() < 5e-4
+
+
+def test_packed_variable_length_sequences(G):
+    """cu_seqlens (the FLA convention the reference block passes through): one row, sequences back to back."""
+    from oracle import c_oracle, gla_ref
+    lens = [130, 1, 64, 700, 65]
+    offs = [0]
+    for n in lens:
+        offs.append(offs[-1] + n)
+    H = 3
+    q, k, v, g = gla_ref.make_inputs(1, offs[-1], H, seed=21)
+    s0 = torch.randn(len(lens), H, 64, 64, generator=torch.Generator().manual_seed(5)) * 0.5
+    o, s = G.chunk_gla(q.cuda(), k.cuda(), v.cuda(), g.cuda(), initial_state=s0.cuda(), output_final_state=True,
+                       cu_seqlens=torch.tensor(offs, dtype=torch.int32))
+    torch.cuda.synchronize()
+    assert s.shape == (len(lens), H, 64, 64)
+    for i, (a, b) in enumerate(zip(offs, offs[1:])):
+        ref, ref_s = c_oracle.forward(q[:, a:b].contiguous(), k[:, a:b].contiguous(), v[:, a:b].contiguous(),
+                                      g[:, a:b].contiguous(), initial_state=s0[i:i + 1], output_final_state=True)
+        _check(ref, o[:, a:b].float().cpu(), relative_abs=True)
+        assert ((s[i:i + 1].cpu() - ref_s).norm() / ref_s.norm()).item() < 5e-4
+    with pytest.raises(ValueError):
+        G.chunk_gla(q.cuda(), k.cuda(), v.cuda(), g.cuda(), cu_seqlens=[0, 10, 5, offs[-1]])
+
+
+def test_short_sequences_and_decoding_with_a_carried_state(G):
+    """The block's `fused_recurrent` call (at most 64 tokens, state cached between calls): pieces of a sequence run one
+    after the other with the state handed on give the outputs and the final state of the whole sequence."""
+    from oracle import c_oracle, gla_ref
+    H, T = 2, 130
+    q, k, v, g = gla_ref.make_inputs(2, T, H, seed=33)
+    ref, ref_s = c_oracle.forward(q, k, v, g, output_final_state=True)
+    qd, kd, vd, gd = (x.cuda() for x in (q, k, v, g))
+    state, outs, a = None, [], 0
+    for n in (64, 1, 1, 37, 27):
+        o, state = G.fused_recurrent_gla(qd[:, a:a + n], kd[:, a:a + n], vd[:, a:a + n], gd[:, a:a + n],
+                                         initial_state=state, output_final_state=True)
+        outs.append(o)
+        a += n
+    torch.cuda.synchronize()
+    _check(ref, torch.cat(outs, dim=1).float().cpu())
+    assert ((state.cpu() - ref_s).norm() / ref_s.norm()).item() < 5e-4
