@@ -35,11 +35,25 @@ class Args(ctypes.Structure):
     ]
 
 
+class BwdArgs(ctypes.Structure):
+    """Mirror of `gla_b200_bwd_args`."""
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("g", ctypes.c_void_p),
+        ("d_o", ctypes.c_void_p),
+        ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p), ("dg", ctypes.c_void_p),
+        ("initial_state", ctypes.c_void_p), ("d_final_state", ctypes.c_void_p), ("d_initial_state", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+        ("B", ctypes.c_int32), ("T", ctypes.c_int32), ("H", ctypes.c_int32), ("K", ctypes.c_int32),
+        ("V", ctypes.c_int32),
+        ("scale", ctypes.c_float),
+    ]
+
+
 EXPORTS = (
     "gla_b200_forward", "gla_b200_workspace_bytes", "gla_b200_check_status", "gla_b200_rmsnorm_gated",
     "gla_b200_trt_enqueue", "gla_b200_strerror", "gla_b200_last_cuda_error", "gla_b200_version",
     "gla_b200_forward_static", "gla_b200_selftest_wait_timeout", "gla_b200_swiglu_dwconv", "gla_b200_layernorm",
-    "gla_b200_stream_probe",
+    "gla_b200_stream_probe", "gla_b200_backward", "gla_b200_backward_workspace_bytes",
 )
 
 _lib = None
@@ -68,6 +82,10 @@ def lib() -> ctypes.CDLL:
     L.gla_b200_selftest_wait_timeout.restype = ctypes.c_int
     L.gla_b200_stream_probe.argtypes = [ctypes.c_void_p, ctypes.c_int64] + [ctypes.c_int32] * 4 + [ctypes.c_void_p] * 2
     L.gla_b200_stream_probe.restype = ctypes.c_int
+    L.gla_b200_backward.argtypes = [ctypes.POINTER(BwdArgs), ctypes.c_void_p]
+    L.gla_b200_backward.restype = ctypes.c_int
+    L.gla_b200_backward_workspace_bytes.argtypes = [ctypes.c_int32] * 5
+    L.gla_b200_backward_workspace_bytes.restype = ctypes.c_size_t
     L.gla_b200_workspace_bytes.argtypes = [ctypes.c_int32] * 5
     L.gla_b200_workspace_bytes.restype = ctypes.c_size_t
     L.gla_b200_check_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]

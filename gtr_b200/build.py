@@ -14,7 +14,7 @@ SRC_DIR = os.path.join(PKG, "csrc")
 SOURCES = [os.path.join(SRC_DIR, "gla_b200.cu")]
 HEADERS = [os.path.join(SRC_DIR, "gla_kernel.cuh"), os.path.join(SRC_DIR, "gla_device.cuh"),
            os.path.join(SRC_DIR, "gla_trace.cuh"),
-           os.path.join(SRC_DIR, "swiglu_dwconv.cuh"),
+           os.path.join(SRC_DIR, "swiglu_dwconv.cuh"), os.path.join(SRC_DIR, "gla_bwd.cuh"),
            os.path.join(ROOT, "include", "gla_b200.h")]
 OUT = os.path.join(PKG, "libgla_b200.so")
 

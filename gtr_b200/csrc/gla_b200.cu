@@ -11,6 +11,7 @@
 
 #include "gla_kernel.cuh"
 #include "swiglu_dwconv.cuh"
+#include "gla_bwd.cuh"
 
 namespace {
 
@@ -581,6 +582,54 @@ int gla_b200_check_status(const void* workspace, void* stream) {
     if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) { note_cuda("status read", e); return GLA_B200_ERR_CUDA; }
     return ctrl[1] == 0 ? GLA_B200_OK : GLA_B200_ERR_TIMEOUT;
+}
+
+size_t gla_b200_backward_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_t K, int32_t V) {
+    if (B <= 0 || T <= 0 || H <= 0 || (K != 32 && K != 64) || V != 64) return 0;
+    const size_t per = align_up(static_cast<size_t>(B) * T * H * K * sizeof(float), 256);
+    return 2 * per + align_up(static_cast<size_t>(B) * H * K * sizeof(float), 256);
+}
+
+int gla_b200_backward(const gla_b200_bwd_args* a, void* stream_v) {
+    if (!a) return GLA_B200_ERR_NULL;
+    if (a->B < 0 || a->T < 0 || a->H <= 0 || (a->K != 32 && a->K != 64) || a->V != 64) return GLA_B200_ERR_SHAPE;
+    if (static_cast<int64_t>(a->B) * a->H > 0x7fffffffLL) return GLA_B200_ERR_SHAPE;
+    if (a->B == 0 || a->T == 0) return GLA_B200_OK;
+    if (!a->q || !a->k || !a->v || !a->g || !a->d_o || !a->dq || !a->dk || !a->dv || !a->dg) return GLA_B200_ERR_NULL;
+    const void* ptrs[] = {a->q, a->k, a->v, a->g, a->d_o, a->dq, a->dk, a->dv, a->dg, a->initial_state, a->d_final_state,
+                          a->d_initial_state, a->workspace};
+    for (const void* p : ptrs)
+        if (p && !aligned16(p)) return GLA_B200_ERR_ALIGN;
+    const size_t need = gla_b200_backward_workspace_bytes(a->B, a->T, a->H, a->K, a->V);
+    if (!a->workspace || a->workspace_bytes < need) return GLA_B200_ERR_WORKSPACE;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { note_cuda("cudaGetDevice", e); return GLA_B200_ERR_CUDA; }
+    DeviceInfo info;
+    if (int rc = device_info(dev, &info)) return rc;
+
+    gla::BwdParams P{};
+    P.q = static_cast<const __half*>(a->q); P.k = static_cast<const __half*>(a->k); P.v = static_cast<const __half*>(a->v);
+    P.g = static_cast<const __half*>(a->g); P.d_o = static_cast<const __half*>(a->d_o);
+    P.dq = static_cast<__half*>(a->dq); P.dk = static_cast<__half*>(a->dk); P.dv = static_cast<__half*>(a->dv);
+    P.dg = a->dg; P.h0 = a->initial_state; P.dht = a->d_final_state; P.dh0 = a->d_initial_state;
+    const size_t per = align_up(static_cast<size_t>(a->B) * a->T * a->H * a->K * sizeof(float), 256);
+    unsigned char* ws = static_cast<unsigned char*>(a->workspace);
+    P.qdq = reinterpret_cast<float*>(ws); P.kdk = reinterpret_cast<float*>(ws + per);
+    P.g_last = a->d_final_state ? reinterpret_cast<float*>(ws + 2 * per) : nullptr;
+    P.B = a->B; P.T = a->T; P.H = a->H; P.scale = a->scale;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const dim3 grid(static_cast<unsigned>(a->B * a->H), 3);
+    if (a->K == 64) {
+        gla::gla_bwd_sweep_kernel<64><<<grid, gla::kBwdThreads, 0, stream>>>(P);
+        gla::gla_bwd_dg_kernel<64><<<grid.x, 1024, 0, stream>>>(P);
+    } else {
+        gla::gla_bwd_sweep_kernel<32><<<grid, gla::kBwdThreads, 0, stream>>>(P);
+        gla::gla_bwd_dg_kernel<32><<<grid.x, 1024, 0, stream>>>(P);
+    }
+    e = cudaPeekAtLastError();
+    if (e != cudaSuccess) { note_cuda("backward launch", e); return GLA_B200_ERR_CUDA; }
+    return GLA_B200_OK;
 }
 
 int gla_b200_rmsnorm_gated(const void* x, const void* g, const void* w, void* y, int64_t rows, int32_t D, float eps,

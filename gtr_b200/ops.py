@@ -1,4 +1,4 @@
-"""Python face of the B200 GLA forward operator.
+"""Python face of the B200 GLA operator (forward, and its gradient for training).
 
 Two call styles are kept so the operator drops in where the reference calls its own:
 
@@ -147,9 +147,18 @@ def chunk_gla_with_ws(q, k, v, gk, scale, ws, **kw) -> torch.Tensor:
     return o
 
 
-def chunk_gla(q, k, v, g, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,
-              output_final_state: bool = False, cu_seqlens=None, *, direction=0, grid_hw=None,
-              gk_normalizer: float = 0.0, segments: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+def _sequence_bounds(cu_seqlens, B: int, T: int):
+    if B != 1:
+        raise ValueError("cu_seqlens needs a batch of one row, as in FLA")
+    offs = [int(x) for x in (cu_seqlens.tolist() if hasattr(cu_seqlens, "tolist") else cu_seqlens)]
+    if len(offs) < 2 or offs[0] != 0 or offs[-1] != T or any(b < a for a, b in zip(offs, offs[1:])):
+        raise ValueError("cu_seqlens must rise from 0 to the row's length")
+    return offs
+
+
+def _chunk_gla_forward(q, k, v, g, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,
+                       output_final_state: bool = False, cu_seqlens=None, *, direction=0, grid_hw=None,
+                       gk_normalizer: float = 0.0, segments: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """FLA-style call: returns (o, final_state).  Allocates output, workspace and final state.
 
     `cu_seqlens` (the FLA convention the reference block passes through, vit_adapter.py:448-451,566-568): a batch of
@@ -160,13 +169,9 @@ def chunk_gla(q, k, v, g, scale: Optional[float] = None, initial_state: Optional
         scale = K ** -0.5
     o = torch.empty(B, T, H, kV, dtype=torch.float16, device=q.device)
     if cu_seqlens is not None:
-        if B != 1:
-            raise ValueError("cu_seqlens needs a batch of one row, as in FLA")
         if direction != 0 or grid_hw is not None:
             raise ValueError("cu_seqlens describes plain forward scans")
-        offs = [int(x) for x in (cu_seqlens.tolist() if hasattr(cu_seqlens, "tolist") else cu_seqlens)]
-        if len(offs) < 2 or offs[0] != 0 or offs[-1] != T or any(b < a for a, b in zip(offs, offs[1:])):
-            raise ValueError("cu_seqlens must rise from 0 to the row's length")
+        offs = _sequence_bounds(cu_seqlens, B, T)
         n = len(offs) - 1
         if initial_state is not None and initial_state.shape[0] != n:
             raise ValueError("initial_state needs one state per sequence")
@@ -182,6 +187,115 @@ def chunk_gla(q, k, v, g, scale: Optional[float] = None, initial_state: Optional
     chunk_gla_run(q, k, v, g, scale, ws, o, gk_normalizer, direction=direction, grid_hw=grid_hw,
                   initial_state=initial_state, final_state=final, segments=segments)
     return o, final
+
+
+def backward_workspace_bytes(B: int, T: int, H: int, K: int = kK) -> int:
+    return int(_lib.lib().gla_b200_backward_workspace_bytes(B, T, H, K, kV))
+
+
+def chunk_gla_backward(q, k, v, g, do, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,
+                       d_final_state: Optional[torch.Tensor] = None, want_d_initial_state: bool = False):
+    """Gradients of `chunk_gla` (row-major scan, log-space gates): returns (dq, dk, dv, dg, d_initial_state) with
+    dq, dk, dv in fp16, dg and the state gradient in fp32.  The reference gets these from FLA's autograd
+    (vit_adapter.py:441,560-568)."""
+    B, T, H, K = q.shape
+    if K not in SUPPORTED_K:
+        raise RuntimeError(f"K must be one of {SUPPORTED_K}")
+    if scale is None:
+        scale = K ** -0.5
+    q, k, v, g, do = (x.contiguous() for x in (q, k, v, g, do))
+    for x, name in ((q, "q"), (k, "k"), (g, "g")):
+        if x.dtype != torch.float16 or not x.is_cuda or tuple(x.shape) != (B, T, H, K):
+            raise RuntimeError(f"{name} must be a CUDA fp16 tensor of shape [B,T,H,K]")
+    for x, name in ((v, "v"), (do, "do")):
+        if x.dtype != torch.float16 or not x.is_cuda or tuple(x.shape) != (B, T, H, kV):
+            raise RuntimeError(f"{name} must be a CUDA fp16 tensor of shape [B,T,H,{kV}]")
+    for x, name in ((initial_state, "initial_state"), (d_final_state, "d_final_state")):
+        if x is not None and (x.dtype != torch.float32 or tuple(x.shape) != (B, H, K, kV) or not x.is_contiguous()):
+            raise RuntimeError(f"{name} must be a contiguous fp32 tensor of shape [B,H,K,{kV}]")
+    dev = q.device
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dg = torch.empty(B, T, H, K, dtype=torch.float32, device=dev)
+    dh0 = torch.empty(B, H, K, kV, dtype=torch.float32, device=dev) if want_d_initial_state else None
+    if B == 0 or T == 0:
+        if dh0 is not None:
+            dh0.copy_(d_final_state) if d_final_state is not None else dh0.zero_()
+        return dq, dk, dv, dg, dh0
+    ws = torch.empty(backward_workspace_bytes(B, T, H, K), dtype=torch.uint8, device=dev)
+    a = _lib.BwdArgs()
+    a.q, a.k, a.v, a.g, a.d_o = (x.data_ptr() for x in (q, k, v, g, do))
+    a.dq, a.dk, a.dv, a.dg = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr()
+    a.initial_state = initial_state.data_ptr() if initial_state is not None else None
+    a.d_final_state = d_final_state.data_ptr() if d_final_state is not None else None
+    a.d_initial_state = dh0.data_ptr() if dh0 is not None else None
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.B, a.T, a.H, a.K, a.V = B, T, H, K, kV
+    a.scale = float(scale)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _lib.check(_lib.lib().gla_b200_backward(ctypes.byref(a), ctypes.c_void_p(stream)))
+    return dq, dk, dv, dg, dh0
+
+
+class _ChunkGLA(torch.autograd.Function):
+    """`chunk_gla` with a gradient: forward and backward are both this library's kernels."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, initial_state, scale, output_final_state, offs, segments):
+        o, final = _chunk_gla_forward(q, k, v, g, scale, initial_state, output_final_state, offs, segments=segments)
+        ctx.save_for_backward(q, k, v, g, initial_state)
+        ctx.scale, ctx.offs = scale, offs
+        if final is None:
+            final = q.new_empty(0, dtype=torch.float32)
+            ctx.mark_non_differentiable(final)
+        return o, final
+
+    @staticmethod
+    def backward(ctx, do, d_final):
+        q, k, v, g, s0 = ctx.saved_tensors
+        if d_final is not None and d_final.numel() == 0:
+            d_final = None
+        want_s0 = s0 is not None and ctx.needs_input_grad[4]
+        if d_final is not None:
+            d_final = d_final.float().contiguous()
+        do = do.to(torch.float16)
+        if ctx.offs is None:
+            dq, dk, dv, dg, ds0 = chunk_gla_backward(q, k, v, g, do, ctx.scale, s0, d_final, want_s0)
+        else:
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            dg = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+            ds0 = torch.empty_like(s0) if want_s0 else None
+            for i, (a, b) in enumerate(zip(ctx.offs, ctx.offs[1:])):
+                part = chunk_gla_backward(q[:, a:b], k[:, a:b], v[:, a:b], g[:, a:b], do[:, a:b], ctx.scale,
+                                          None if s0 is None else s0[i:i + 1].contiguous(),
+                                          None if d_final is None else d_final[i:i + 1], want_s0)
+                dq[:, a:b], dk[:, a:b], dv[:, a:b], dg[:, a:b] = part[:4]
+                if want_s0:
+                    ds0[i:i + 1] = part[4]
+        return dq, dk, dv, dg.to(g.dtype), ds0, None, None, None, None
+
+
+def chunk_gla(q, k, v, g, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,
+              output_final_state: bool = False, cu_seqlens=None, *, direction=0, grid_hw=None,
+              gk_normalizer: float = 0.0, segments: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """FLA-style call (vit_adapter.py:566-568): returns (o, final_state); `_chunk_gla_forward` documents the arguments.
+    When gradients are enabled and an input requires one, the call is recorded for autograd and its backward runs
+    `chunk_gla_backward` -- as FLA's operator does for the reference in training.  That path serves the plain row-major
+    scan with log-space gates (what FLA's signature expresses); the scan directions and the raw-logit gate mode are
+    inference features."""
+    tensors = [x for x in (q, k, v, g, initial_state) if x is not None]
+    if not (torch.is_grad_enabled() and any(x.requires_grad for x in tensors)):
+        return _chunk_gla_forward(q, k, v, g, scale, initial_state, output_final_state, cu_seqlens, direction=direction,
+                                  grid_hw=grid_hw, gk_normalizer=gk_normalizer, segments=segments)
+    if _direction_id(direction) != 0 or gk_normalizer > 0.0:
+        raise RuntimeError("the gradient is implemented for direction 0 and log-space gates; apply logsigmoid and the "
+                           "token order in PyTorch around the call when training")
+    B, T, H, K = q.shape
+    if scale is None:
+        scale = K ** -0.5
+    offs = None if cu_seqlens is None else _sequence_bounds(cu_seqlens, B, T)
+    o, final = _ChunkGLA.apply(q, k, v, g, initial_state, float(scale), bool(output_final_state), offs, int(segments))
+    return o, (final if output_final_state else None)
 
 
 def fused_recurrent_gla(q, k, v, gk, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,

@@ -135,6 +135,39 @@ int gla_b200_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint
 int gla_b200_stream_probe(const void* buf, int64_t rows, int32_t heads, int32_t ctas, int32_t tiles, int32_t chunks,
                           int32_t* status, void* stream);
 
+/* Gradient of the plain operator (row-major scan, log-space gates), for training.  The reference has no CUDA gradient
+ * of its own: its training path calls the third-party FLA operator and relies on that operator's autograd
+ * (engine/gtr/backbone/vit_adapter.py:441,560-568; flash-linear-attention 0.5.0, requirements.txt:9).  This entry point
+ * is what an autograd wrapper around gla_b200_forward calls in its backward.
+ *   q, k, g : fp16 [B,T,H,K]   v, d_o : fp16 [B,T,H,V]   contiguous   ->   dq, dk : fp16 [B,T,H,K]   dv : fp16 [B,T,H,V]
+ *   dg : fp32 [B,T,H,K] (the caller casts)   states and their gradients: fp32 [B,H,K,V], each optional (NULL).
+ * With S_t = exp(g_t) S_{t-1} + k_t v_t^T, o_t = scale q_t^T S_t:
+ *   dS_t = exp(g_{t+1}) dS_{t+1} + scale q_t do_t^T,  dq_t = scale S_t do_t,  dk_t = dS_t v_t,  dv_t = dS_t^T k_t,
+ *   dg_t = sum_{s>=t} (q_s dq_s - k_s dk_s) (+ sum_v d_final_state * final_state at the last token),
+ *   d_initial_state = exp(g_1) dS_1.
+ * Never synchronises or allocates; the workspace needs no clearing. */
+typedef struct gla_b200_bwd_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    const void* g;
+    const void* d_o;
+    void* dq;
+    void* dk;
+    void* dv;
+    float* dg;
+    const float* initial_state;      /* the forward call's initial state, or NULL */
+    const float* d_final_state;      /* gradient flowing into the forward call's final state, or NULL */
+    float* d_initial_state;          /* out, or NULL */
+    void* workspace;                 /* >= gla_b200_backward_workspace_bytes(B,T,H,K,V), 256-byte aligned */
+    size_t workspace_bytes;
+    int32_t B, T, H, K, V;
+    float scale;
+} gla_b200_bwd_args;
+
+size_t gla_b200_backward_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_t K, int32_t V);
+int gla_b200_backward(const gla_b200_bwd_args* args, void* stream);
+
 /* Replaces rmsnorm_gated (gla_torch_ext.cu:156-196, kernel gla_norm_gate.cuh:13-75):
  * y = x * rsqrt(mean(x^2) + eps) * w * silu(g) over rows of D = 64 fp16 values; y may alias x. */
 int gla_b200_rmsnorm_gated(const void* x, const void* g, const void* w, void* y,

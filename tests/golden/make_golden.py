@@ -21,6 +21,9 @@ What is executed from the reference (imported, never copied):
     tensorrt_plugin/gtr_onnx_patches.py:94-96 state).  Weights are random, rounded to fp16 so that the fixture can
     store them in half the space; the fixture holds the state dict, the input and the three returned feature maps.
 
+  * engine/gtr/backbone/csrc/test_gla.py : `_recurrence_fp64` once more, under torch autograd, for the gradients of
+    the recurrence (recurrence_backward.npz; `--backward-only` regenerates just that file).
+
     python tests/golden/make_golden.py /path/to/GTR
 """
 from __future__ import annotations
@@ -105,6 +108,27 @@ def recurrence_cases(ref_root: str):
         for n, x in (("q", q), ("k", k), ("v", v)):
             out[f"k{K}_m1000_{n}"] = x.numpy()
         out[f"k{K}_m1000_o"] = o.float().numpy()
+    return out
+
+
+def backward_cases(ref_root: str):
+    """Gradients of the reference's own float64 recurrence (`test_gla._recurrence_fp64`) by torch autograd: the
+    reference trains through a third-party operator's autograd, so the gradient of its own statement of the
+    recurrence is the vector to hold the backward kernels to."""
+    out = {}
+    for K in (64, 32):
+        ref = load_reference_test_module(ref_root, K)
+        for gates, (B, T, H) in (("weak", (1, 70, 2)), ("strong", (1, 40, 1))):
+            q, k, v, g = ref._inputs(B, T, H, seed=1, gates=gates)
+            do = torch.randn(v.shape, generator=torch.Generator().manual_seed(7)).to(v.dtype)
+            leaves = [x.detach().double().requires_grad_(True) for x in (q, k, v, g)]
+            o = ref._recurrence_fp64(*leaves)
+            grads = torch.autograd.grad((o * do.double()).sum(), leaves)
+            tag = f"k{K}_{gates}"
+            for n, x in (("q", q), ("k", k), ("v", v), ("g", g), ("do", do)):
+                out[f"{tag}_{n}"] = x.numpy()
+            for n, x in zip(("dq", "dk", "dv", "dg"), grads):
+                out[f"{tag}_{n}"] = x.float().numpy()
     return out
 
 
@@ -193,6 +217,9 @@ def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: python make_golden.py <path to a checkout of the GTR reference>")
     ref_root = sys.argv[1]
+    np.savez_compressed(os.path.join(HERE, "recurrence_backward.npz"), **backward_cases(ref_root))
+    if "--backward-only" in sys.argv:
+        return
     np.savez_compressed(os.path.join(HERE, "recurrence_fp64.npz"), **recurrence_cases(ref_root))
     try:
         np.savez_compressed(os.path.join(HERE, "scan_order.npz"), **scan_order_cases(ref_root))
