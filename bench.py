@@ -167,7 +167,7 @@ def more_cpu_baselines(budget_s=4.0):
     return out
 
 
-def fla_triton_comparator(timeout_s=150):
+def fla_triton_comparator(timeout_s=200):
     """flash-linear-attention's Triton chunk_gla (what the reference falls back to at K = 64) on this GPU, c3 shape.
     Run in a child process with a time limit (a Triton build can take a while); context only, never the target."""
     code = r"""
@@ -183,14 +183,29 @@ e0.record()
 for _ in range(20): o, _ = chunk_gla(q, k, v, g)
 e1.record(); torch.cuda.synchronize()
 us = e0.elapsed_time(e1) * 1000 / 20
-print(json.dumps({'us_per_forward': us, 'tokens_per_s': q.shape[0] * q.shape[1] / (us * 1e-6), 'finite': bool(torch.isfinite(o).all())}))
+res = {'us_per_forward': us, 'tokens_per_s': q.shape[0] * q.shape[1] / (us * 1e-6), 'finite': bool(torch.isfinite(o).all())}
+print(json.dumps(res), flush=True)
+leaves = [x.clone().requires_grad_(True) for x in (q, k, v, g)]
+do = torch.randn_like(v)
+def both():
+    o, _ = chunk_gla(*leaves)
+    o.backward(do)
+for _ in range(3): both()
+torch.cuda.synchronize()
+e0.record()
+for _ in range(10): both()
+e1.record(); torch.cuda.synchronize()
+res['us_forward_and_backward'] = e0.elapsed_time(e1) * 1000 / 10
+print(json.dumps(res), flush=True)
 """ % ROOT
     try:
         run = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=timeout_s)
-        if run.returncode != 0:
+        lines = [l for l in run.stdout.strip().splitlines() if l.startswith("{")]
+        if not lines:
             return {"unavailable": (run.stderr.strip().splitlines() or ["failed"])[-1][:200]}
-        res = json.loads(run.stdout.strip().splitlines()[-1])
-        res["what"] = "fla.ops.gla.chunk_gla (Triton), c3 shape, 20 forwards back to back, inputs L2-resident between calls"
+        res = json.loads(lines[-1])          # the forward figure stands even if the backward leg fails to build
+        res["what"] = ("fla.ops.gla.chunk_gla (Triton), c3 shape, 20 forwards back to back, inputs L2-resident between calls; "
+                       "then 10 forward + backward pairs through its autograd")
         return res
     except subprocess.TimeoutExpired:
         return {"unavailable": f"no result within {timeout_s} s"}
@@ -338,6 +353,24 @@ def extra_workload(gtr_b200, name, dev, peak):
             "input_sets": len(sets), "finite": bool(torch.isfinite(o).all())}
 
 
+def extra_gradient(gtr_b200, name, dev):
+    """The operator's gradient (gla_b200_backward: dq, dk, dv, dg) on a configuration's shape: time per call and one
+    sequence of it checked against the float64 oracle."""
+    from oracle import gla_bwd_ref
+    q, k, v, g = (x.to(dev) for x in workloads.config_inputs(name, seed=77))
+    B, T, H, K = q.shape
+    do = (torch.randn(B, T, H, 64, generator=torch.Generator().manual_seed(78)) / 8).half().to(dev)
+    fn = lambda i: gtr_b200.chunk_gla_backward(q, k, v, g, do)
+    total_ms, per = time_forwards(fn, steps=10, inner=2, warmup_steps=3, sync=torch.cuda.synchronize)
+    n = min(T, 512)
+    got = gtr_b200.chunk_gla_backward(q[:1, :n], k[:1, :n], v[:1, :n], g[:1, :n], do[:1, :n])
+    want = gla_bwd_ref.recurrent_gla_backward(q[:1, :n].cpu(), k[:1, :n].cpu(), v[:1, :n].cpu(), g[:1, :n].cpu(), do[:1, :n].cpu())
+    rel = [float((a.double().cpu() - b).norm() / b.norm()) for a, b in zip(got[:4], want[:4])]
+    return {"workload": WORKLOADS[name], "us_per_call": percentiles(per), "tokens_per_s": B * T / (statistics.mean(per) * 1e-6),
+            "kernels_per_call": 4 if T >= 512 and 3 * B * H < 600 else 2,
+            "rel_l2_vs_oracle": dict(zip(("dq", "dk", "dv", "dg"), rel)), "checked": f"first {n} tokens of sequence 0"}
+
+
 def extra_gated(gtr_b200, dev, peak, B, T, H, grid, label):
     """The call a backbone block makes: q, k, v, output gate and raw gate logits are strided views of one packed
     projection buffer, logsigmoid(x)/16 is applied in the kernel, RMSNorm * w * silu(gate) is fused."""
@@ -420,6 +453,18 @@ def run_ours(args, rank, local_rank, world):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.profile_backward > 0:
+        # a short run for a profiler: the gradient call on the workload's shape
+        q, k, v, g = dev_sets[0]
+        do = torch.randn(B, T, H, 64, device=dev).half()
+        for _ in range(args.warmup + args.profile_backward):
+            gtr_b200.chunk_gla_backward(q, k, v, g, do)
+        torch.cuda.synchronize()
+        if rank == 0:
+            print(json.dumps({"profile_backward": args.profile_backward, "warmup_calls": args.warmup,
+                              "config": workload_config(args.workload, B, H, T, K)}))
+        return
 
     if args.profile_forwards > 0:
         # a short run for a profiler: the same forwards on the same inputs, no one-second warm-up, nothing else
@@ -585,6 +630,10 @@ def run_ours(args, rank, local_rank, world):
                                     "configs[3]'s per-block call at 1 GPU (B32 T8192 H12), fused epilogue + raw gate logits")]
                 except Exception as e:
                     extra["gated"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+                try:
+                    extra["gradient"] = [extra_gradient(gtr_b200, w, dev) for w in ("c3", "c2")]
+                except Exception as e:
+                    extra["gradient"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
                 extra["cpu_baselines"] = more_cpu_baselines()
                 extra["fla_triton_chunk_gla"] = fla_triton_comparator()
         tokens_per_step = B * T * inner
@@ -633,6 +682,8 @@ def main():
                     help="run only the backbone leg (--backbone-batch, --backbone-steps) and exit (for ncu)")
     ap.add_argument("--profile-forwards", type=int, default=0,
                     help="run only warmup + N forwards of the workload (for ncu) and exit")
+    ap.add_argument("--profile-backward", type=int, default=0,
+                    help="run this many gradient calls (gla_b200_backward) on the workload after --warmup calls, then exit")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     args = ap.parse_args()

@@ -3,6 +3,7 @@
 // synchronisation on the forward path.
 #include "gla_b200.h"
 
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -584,10 +585,25 @@ int gla_b200_check_status(const void* workspace, void* stream) {
     return ctrl[1] == 0 ? GLA_B200_OK : GLA_B200_ERR_TIMEOUT;
 }
 
+// Segments per sequence for the gradient sweeps: enough CTAs to give every SM several (the sweeps hide latency by
+// occupancy), segments of at least 256 tokens.  A pure function of the shape, so the workspace size can be asked ahead.
+static int bwd_segments(int B, int T, int H, int* seg_len) {
+    const int64_t ctas = 3LL * B * H;
+    int nseg = static_cast<int>((600 + ctas - 1) / ctas);
+    nseg = std::max(1, std::min(nseg, T / 256));
+    int len = ((T + nseg - 1) / nseg + 31) / 32 * 32;
+    nseg = (T + len - 1) / len;
+    *seg_len = nseg > 1 ? len : std::max(T, 1);
+    return nseg;
+}
+
 size_t gla_b200_backward_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_t K, int32_t V) {
     if (B <= 0 || T <= 0 || H <= 0 || (K != 32 && K != 64) || V != 64) return 0;
     const size_t per = align_up(static_cast<size_t>(B) * T * H * K * sizeof(float), 256);
-    return 2 * per + align_up(static_cast<size_t>(B) * H * K * sizeof(float), 256);
+    int seg_len = 0;
+    const size_t nseg = static_cast<size_t>(bwd_segments(B, T, H, &seg_len));
+    const size_t seg = nseg > 1 ? align_up(2 * static_cast<size_t>(B) * H * nseg * K * (64 + 1) * sizeof(float), 256) : 0;
+    return 2 * per + align_up(static_cast<size_t>(B) * H * K * sizeof(float), 256) + seg;
 }
 
 int gla_b200_backward(const gla_b200_bwd_args* a, void* stream_v) {
@@ -618,15 +634,25 @@ int gla_b200_backward(const gla_b200_bwd_args* a, void* stream_v) {
     P.qdq = reinterpret_cast<float*>(ws); P.kdk = reinterpret_cast<float*>(ws + per);
     P.g_last = a->d_final_state ? reinterpret_cast<float*>(ws + 2 * per) : nullptr;
     P.B = a->B; P.T = a->T; P.H = a->H; P.scale = a->scale;
+    P.nseg = bwd_segments(a->B, a->T, a->H, &P.seg_len);
+    const size_t last = align_up(static_cast<size_t>(a->B) * a->H * a->K * sizeof(float), 256);
+    P.seg_state = reinterpret_cast<float*>(ws + 2 * per + last);
+    P.seg_decay = P.seg_state + 2 * static_cast<size_t>(a->B) * a->H * P.nseg * a->K * 64;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    const dim3 grid(static_cast<unsigned>(a->B * a->H), 3);
-    if (a->K == 64) {
-        gla::gla_bwd_sweep_kernel<64><<<grid, gla::kBwdThreads, 0, stream>>>(P);
-        gla::gla_bwd_dg_kernel<64><<<grid.x, 1024, 0, stream>>>(P);
-    } else {
-        gla::gla_bwd_sweep_kernel<32><<<grid, gla::kBwdThreads, 0, stream>>>(P);
-        gla::gla_bwd_dg_kernel<32><<<grid.x, 1024, 0, stream>>>(P);
-    }
+    const unsigned bh = static_cast<unsigned>(a->B * a->H);
+    if (static_cast<int64_t>(bh) * P.nseg > 0x7fffffffLL) return GLA_B200_ERR_SHAPE;
+#define GLA_BWD_LAUNCH(KK)                                                                                            \
+    do {                                                                                                              \
+        if (P.nseg > 1) {                                                                                             \
+            gla::gla_bwd_state_kernel<KK><<<dim3(bh * (P.nseg - 1), 2), gla::kBwdThreads, 0, stream>>>(P);            \
+            gla::gla_bwd_combine_kernel<KK><<<dim3(bh, 2), 256, 0, stream>>>(P);                                      \
+        }                                                                                                             \
+        gla::gla_bwd_sweep_kernel<KK><<<dim3(bh * P.nseg, 3), gla::kBwdThreads, 0, stream>>>(P);                      \
+        gla::gla_bwd_dg_kernel<KK><<<bh, 1024, 0, stream>>>(P);                                                       \
+    } while (0)
+    if (a->K == 64) GLA_BWD_LAUNCH(64);
+    else GLA_BWD_LAUNCH(32);
+#undef GLA_BWD_LAUNCH
     e = cudaPeekAtLastError();
     if (e != cudaSuccess) { note_cuda("backward launch", e); return GLA_B200_ERR_CUDA; }
     return GLA_B200_OK;

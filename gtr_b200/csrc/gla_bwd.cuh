@@ -7,10 +7,11 @@
 //
 // The reference trains through the third-party FLA operator (engine/gtr/backbone/vit_adapter.py:441,560-568); its
 // own CUDA extension has no gradient.  Three independent sweeps run as three kinds of CTA per (batch, head):
-//   kind 0  walks forward with S (a thread owns one key row and a slice of the value columns) and emits dq;
-//   kind 1  walks backward with dS in the same ownership and emits dk (and d initial_state);
-//   kind 2  walks backward with a second copy of dS owned by value column, and emits dv,
-// so that every per-token reduction is inside a thread plus one or two shuffles.  Tokens are staged 32 at a time:
+//   kind 0  walks forward with S and emits dq;
+//   kind 1  walks backward with dS and emits dk (and d initial_state);
+//   kind 2  walks backward with a second copy of dS, blocked the other way round, and emits dv.
+// A thread owns a small block of the state, so a token costs it 6 or 7 shared-memory reads of 16 bytes, and every
+// per-token reduction is inside the thread plus a 3-step butterfly over 8 lanes.  Tokens are staged 32 at a time:
 // the next chunk's fp16 rows are fetched into registers while the current chunk is worked from fp32 tiles in
 // shared memory.  A last kernel turns the per-token products q dq - k dk into dg by a reverse running sum.
 // All arithmetic is fp32 on CUDA cores, two lanes per instruction (fma.rn.f32x2): 1.5 instructions per state element and
@@ -33,7 +34,10 @@ struct BwdParams {
     float* dh0;           // [B,H,K,64] or null
     float *qdq, *kdk;     // scratch [B,T,H,K]
     float* g_last;        // scratch [B,H,K]: sum_v dht * final_state
+    float* seg_state;     // scratch [2][B*H][nseg][K,64]: a segment's own contribution, then the state it starts from
+    float* seg_decay;     // scratch [2][B*H][nseg][K]: product of the gates over a segment
     int B, T, H;
+    int nseg, seg_len;    // a sequence is cut into nseg pieces of seg_len tokens (a multiple of 32), each its own CTA
     float scale;
 };
 
@@ -97,17 +101,61 @@ struct BwdSmem {
     __half raw[kBwdChunk * 64];
 };
 
-// Kinds 0 and 1.  A thread owns row `row` of the K x 64 state and NV of its columns.
+// Sum over the 8 lanes of a group (lane bits 0..2) of R values each lane holds, by a butterfly that halves the values
+// kept at every exchange: 4 shuffles for R = 4, 3 for R = 2.  Every lane ends with the complete sum of value `which`.
+template <int R>
+__device__ __forceinline__ float bwd_reduce8(const float (&v)[R], int lane, int& which) {
+    constexpr unsigned kAll = 0xffffffffu;
+    const bool b2 = (lane & 4) != 0, b1 = (lane & 2) != 0;
+    float k;
+    if (R == 4) {
+        float k0 = b2 ? v[R - 2] : v[0], k1 = b2 ? v[R - 1] : v[1];
+        const float s0 = b2 ? v[0] : v[R - 2], s1 = b2 ? v[1] : v[R - 1];
+        k0 += __shfl_xor_sync(kAll, s0, 4);
+        k1 += __shfl_xor_sync(kAll, s1, 4);
+        k = b1 ? k1 : k0;
+        k += __shfl_xor_sync(kAll, b1 ? k0 : k1, 2);
+        which = (b2 ? 2 : 0) + (b1 ? 1 : 0);
+    } else {
+        k = b2 ? v[R - 1] : v[0];
+        k += __shfl_xor_sync(kAll, b2 ? v[0] : v[R - 1], 4);
+        k += __shfl_xor_sync(kAll, k, 2);
+        which = b2 ? 1 : 0;
+    }
+    k += __shfl_xor_sync(kAll, k, 1);
+    return k;
+}
+
+template <int N>
+__device__ __forceinline__ void bwd_lds(float (&d)[N], const float* src) {
+    if (N == 2) {
+        const float2 u = *reinterpret_cast<const float2*>(src);
+        d[0] = u.x; d[1] = u.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) {
+            const float4 u = reinterpret_cast<const float4*>(src)[i];
+            d[4 * i] = u.x; d[4 * i + 1] = u.y; d[4 * i + 2] = u.z; d[4 * i + 3] = u.w;
+        }
+    }
+}
+
+// Kinds 0 and 1.  A thread owns an R x 8 block of the K x 64 state (R = K / 16): 16 row groups x 8 column groups, the 8
+// column groups of a row group in neighbouring lanes.  Per token it reads its R gates and key-side factors and its 8 + 8
+// value-side entries (6 shared-memory reads of 16 bytes), and the R row sums are completed across the 8 lanes.
 //   kind 0 (forward in t):   S = a S + b x ,  acc = S . y     a = exp(g_t), b = k_t,        x = v_t,  y = do_t
 //   kind 1 (backward in t):  S = S + b x ,    acc = S . y ,  S = a S     a = exp(g_t), b = scale q_t, x = do_t, y = v_t
-template <int K, int kKind>
-__device__ void bwd_row_sweep(const BwdParams& P, BwdSmem& sm, int bh) {
-    constexpr int kParts = kBwdThreads / K, NV = 64 / kParts;
+// With kStateOnly the sweep starts from zero, emits nothing per token and leaves the segment's own contribution to the
+// state, and the product of its gates, for gla_bwd_combine_kernel.
+template <int K, int kKind, bool kStateOnly>
+__device__ void bwd_row_sweep(const BwdParams& P, BwdSmem& sm, int bh, int seg) {
+    constexpr int R = K / 16;
     constexpr bool kFwd = kKind == 0;
-    const int tid = threadIdx.x, row = tid / kParts, part = tid % kParts;
-    const int b = bh / P.H, h = bh % P.H, T = P.T;
+    const int tid = threadIdx.x, lane = tid & 31, cg = tid & 7, rg = tid >> 3;
+    const int b = bh / P.H, h = bh % P.H;
+    const int t_begin = seg * P.seg_len, T = min(P.T, t_begin + P.seg_len);        // this CTA's tokens: [t_begin, T)
     const int64_t strideK = static_cast<int64_t>(P.H) * K, strideV = static_cast<int64_t>(P.H) * 64;
-    const int64_t offK = (static_cast<int64_t>(b) * T * P.H + h) * K, offV = (static_cast<int64_t>(b) * T * P.H + h) * 64;
+    const int64_t offK = (static_cast<int64_t>(b) * P.T * P.H + h) * K, offV = (static_cast<int64_t>(b) * P.T * P.H + h) * 64;
     const __half* pa = P.g + offK;                                  // gate
     const __half* pb = (kFwd ? P.k : P.q) + offK;                   // the rank-one update's key-side factor
     const __half* px = (kFwd ? P.v : P.d_o) + offV;                 // its value-side factor
@@ -115,66 +163,90 @@ __device__ void bwd_row_sweep(const BwdParams& P, BwdSmem& sm, int bh) {
     const __half* pr = (kFwd ? P.q : P.k) + offK;                   // the factor of the gate-gradient product
     __half* pout = (kFwd ? P.dq : P.dk) + offK;
     float* pprod = (kFwd ? P.qdq : P.kdk) + offK;
+    const int block_off = R * rg * 64 + 8 * cg;                     // this thread's block inside a [K,64] state
+    const int64_t state_off = static_cast<int64_t>(bh) * K * 64 + block_off;
+    const int64_t seg_slot = (static_cast<int64_t>(kFwd ? 0 : P.B * P.H) + bh) * P.nseg + seg;
 
-    float2 S[NV / 2];
-    const float* init = kFwd ? P.h0 : P.dht;
+    float2 S[R][4];
+    float decay[R];
+    const float* init = kStateOnly ? nullptr
+                        : P.nseg > 1 ? P.seg_state + seg_slot * K * 64 + block_off
+                        : (kFwd ? P.h0 : P.dht) ? (kFwd ? P.h0 : P.dht) + state_off : nullptr;
 #pragma unroll
-    for (int j = 0; j < NV / 2; ++j) {
-        const float* src = init + (static_cast<int64_t>(bh) * K + row) * 64 + part * NV + 2 * j;
-        S[j] = init ? make_float2(src[0], src[1]) : make_float2(0.f, 0.f);
+    for (int r = 0; r < R; ++r) {
+        decay[r] = 1.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            S[r][c] = init ? *reinterpret_cast<const float2*>(init + r * 64 + 2 * c) : make_float2(0.f, 0.f);
     }
 
-    const int nchunks = (T + kBwdChunk - 1) / kBwdChunk;
+    const int nchunks = (T - t_begin + kBwdChunk - 1) / kBwdChunk;
     uint4 ra[K / 32], rb[K / 32], rr[K / 32], rx[2], ry[2];
     auto fetch = [&](int ci) {
-        const int t0 = (kFwd ? ci : nchunks - 1 - ci) * kBwdChunk;
+        const int t0 = t_begin + (kFwd ? ci : nchunks - 1 - ci) * kBwdChunk;
         bwd_fetch<K>(ra, pa, strideK, t0, T, tid);
         bwd_fetch<K>(rb, pb, strideK, t0, T, tid);
-        bwd_fetch<K>(rr, pr, strideK, t0, T, tid);
         bwd_fetch<64>(rx, px, strideV, t0, T, tid);
-        bwd_fetch<64>(ry, py, strideV, t0, T, tid);
+        if (!kStateOnly) {
+            bwd_fetch<K>(rr, pr, strideK, t0, T, tid);
+            bwd_fetch<64>(ry, py, strideV, t0, T, tid);
+        }
     };
     if (nchunks > 0) fetch(0);
     for (int ci = 0; ci < nchunks; ++ci) {
-        const int t0 = (kFwd ? ci : nchunks - 1 - ci) * kBwdChunk;
+        const int t0 = t_begin + (kFwd ? ci : nchunks - 1 - ci) * kBwdChunk;
         bwd_spread<K, true>(sm.tile[0], ra, 1.f, tid);
         bwd_spread<K, false>(sm.tile[1], rb, kFwd ? 1.f : P.scale, tid);
         bwd_spread<64, false>(sm.tile[2], rx, 1.f, tid);
-        bwd_spread<64, false>(sm.tile[3], ry, 1.f, tid);
-        bwd_keep<K>(sm.raw, rr, tid);
+        if (!kStateOnly) {
+            bwd_spread<64, false>(sm.tile[3], ry, 1.f, tid);
+            bwd_keep<K>(sm.raw, rr, tid);
+        }
         __syncthreads();
         if (ci + 1 < nchunks) fetch(ci + 1);
-#pragma unroll 2
+#pragma unroll 4
         for (int tt = 0; tt < kBwdChunk; ++tt) {
             const int t = kFwd ? tt : kBwdChunk - 1 - tt;
-            const float a = sm.tile[0][t * K + row], bq = sm.tile[1][t * K + row];
-            const float4* X = reinterpret_cast<const float4*>(&sm.tile[2][t * 64 + part * NV]);
-            const float4* Y = reinterpret_cast<const float4*>(&sm.tile[3][t * 64 + part * NV]);
-            const float2 aa = make_float2(a, a), bb = make_float2(bq, bq);
-            float2 acc2 = make_float2(0.f, 0.f);
+            float a[R], bq[R], x[8], y[8], v[R];
+            bwd_lds<R>(a, &sm.tile[0][t * K + R * rg]);
+            bwd_lds<R>(bq, &sm.tile[1][t * K + R * rg]);
+            bwd_lds<8>(x, &sm.tile[2][t * 64 + 8 * cg]);
+            if (kStateOnly) {
 #pragma unroll
-            for (int j = 0; j < NV / 4; ++j) {
-                const float4 x = X[j], y = Y[j];
-                const float2 x0 = make_float2(x.x, x.y), x1 = make_float2(x.z, x.w);
-                const float2 y0 = make_float2(y.x, y.y), y1 = make_float2(y.z, y.w);
-                if (kFwd) {
-                    S[2 * j] = bwd_fma2(S[2 * j], aa, bwd_mul2(bb, x0));
-                    S[2 * j + 1] = bwd_fma2(S[2 * j + 1], aa, bwd_mul2(bb, x1));
-                } else {
-                    S[2 * j] = bwd_fma2(bb, x0, S[2 * j]);
-                    S[2 * j + 1] = bwd_fma2(bb, x1, S[2 * j + 1]);
+                for (int r = 0; r < R; ++r) {
+                    const float2 aa = make_float2(a[r], a[r]), bb = make_float2(bq[r], bq[r]);
+                    decay[r] *= a[r];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float2 x2 = make_float2(x[2 * c], x[2 * c + 1]);
+                        if (kFwd) S[r][c] = bwd_fma2(S[r][c], aa, bwd_mul2(bb, x2));
+                        else S[r][c] = bwd_mul2(bwd_fma2(bb, x2, S[r][c]), aa);
+                    }
                 }
-                acc2 = bwd_fma2(S[2 * j], y0, acc2);
-                acc2 = bwd_fma2(S[2 * j + 1], y1, acc2);
-                if (!kFwd) {
-                    S[2 * j] = bwd_mul2(S[2 * j], aa);
-                    S[2 * j + 1] = bwd_mul2(S[2 * j + 1], aa);
-                }
+                continue;
             }
-            float acc = acc2.x + acc2.y;
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            if (kParts == 4) acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (part == 0) sm.out[t * K + row] = acc;
+            bwd_lds<8>(y, &sm.tile[3][t * 64 + 8 * cg]);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float2 aa = make_float2(a[r], a[r]), bb = make_float2(bq[r], bq[r]);
+                float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float2 x2 = make_float2(x[2 * c], x[2 * c + 1]), y2 = make_float2(y[2 * c], y[2 * c + 1]);
+                    if (kFwd) S[r][c] = bwd_fma2(S[r][c], aa, bwd_mul2(bb, x2));
+                    else S[r][c] = bwd_fma2(bb, x2, S[r][c]);
+                    acc = bwd_fma2(S[r][c], y2, acc);
+                    if (!kFwd) S[r][c] = bwd_mul2(S[r][c], aa);
+                }
+                v[r] = acc.x + acc.y;
+            }
+            int which;
+            const float sum = bwd_reduce8<R>(v, lane, which);
+            if (!(lane & 1)) sm.out[t * K + R * rg + which] = sum;
+        }
+        if (kStateOnly) {
+            __syncthreads();
+            continue;
         }
         __syncthreads();
         // the chunk's gradient rows, and their products with q (k) for the gate gradient
@@ -206,50 +278,71 @@ __device__ void bwd_row_sweep(const BwdParams& P, BwdSmem& sm, int bh) {
         }
         __syncthreads();
     }
-    if (kFwd) {
-        if (P.g_last) {                      // S is the final state here
-            float acc = 0.f;
-            if (P.dht) {
+    if (kStateOnly) {
 #pragma unroll
-                for (int j = 0; j < NV / 2; ++j) {
-                    const float* d = P.dht + (static_cast<int64_t>(bh) * K + row) * 64 + part * NV + 2 * j;
-                    acc = fmaf(d[0], S[j].x, fmaf(d[1], S[j].y, acc));
-                }
-            }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            if (kParts == 4) acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (part == 0) P.g_last[static_cast<int64_t>(bh) * K + row] = acc;
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<float2*>(P.seg_state + seg_slot * K * 64 + block_off + r * 64 + 2 * c) = S[r][c];
+            if (cg == 0) P.seg_decay[seg_slot * K + R * rg + r] = decay[r];
         }
-    } else if (P.dh0) {
+    } else if (kFwd) {
+        if (P.g_last && seg == P.nseg - 1) {                      // S is the final state here
+            float v[R];
 #pragma unroll
-        for (int j = 0; j < NV / 2; ++j)
-            *reinterpret_cast<float2*>(P.dh0 + (static_cast<int64_t>(bh) * K + row) * 64 + part * NV + 2 * j) = S[j];
+            for (int r = 0; r < R; ++r) {
+                float acc = 0.f;
+                if (P.dht) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float2 d = *reinterpret_cast<const float2*>(P.dht + state_off + r * 64 + 2 * c);
+                        acc = fmaf(d.x, S[r][c].x, fmaf(d.y, S[r][c].y, acc));
+                    }
+                }
+                v[r] = acc;
+            }
+            int which;
+            const float sum = bwd_reduce8<R>(v, lane, which);
+            if (!(lane & 1)) P.g_last[static_cast<int64_t>(bh) * K + R * rg + which] = sum;
+        }
+    } else if (P.dh0 && seg == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) *reinterpret_cast<float2*>(P.dh0 + state_off + r * 64 + 2 * c) = S[r][c];
     }
 }
 
-// Kind 2.  A thread owns value column `col` of dS and NC of its key rows:
-//   S = S + bq x ,  acc = S . kk ,  S = a S      a = exp(g_t), bq = scale q_t, kk = k_t (vectors over the rows),  x = do_t[col]
+// Kind 2.  A thread owns a (K / 8) x 4 block of dS: 8 row groups in neighbouring lanes x 16 column groups.  Its rows are
+// 4 rg .. 4 rg + 3 (and 32 + the same for K = 64), so that the 8 lanes' 16-byte reads of the key-side tiles fall on distinct
+// banks.  The 4 column sums are completed across the 8 lanes.
+//   S = S + bq x ,  acc = S^T kk ,  S = a S      a = exp(g_t), bq = scale q_t, kk = k_t (over the rows),  x = do_t (over the columns)
 template <int K>
-__device__ void bwd_col_sweep(const BwdParams& P, BwdSmem& sm, int bh) {
-    constexpr int NC = K / 2;
-    const int tid = threadIdx.x, col = tid >> 1, part = tid & 1;
-    const int b = bh / P.H, h = bh % P.H, T = P.T;
+__device__ void bwd_col_sweep(const BwdParams& P, BwdSmem& sm, int bh, int seg) {
+    constexpr int RC = K / 8;
+    const int tid = threadIdx.x, lane = tid & 31, rg = tid & 7, cg = tid >> 3;
+    const int b = bh / P.H, h = bh % P.H;
+    const int t_begin = seg * P.seg_len, T = min(P.T, t_begin + P.seg_len);
     const int64_t strideK = static_cast<int64_t>(P.H) * K, strideV = static_cast<int64_t>(P.H) * 64;
-    const int64_t offK = (static_cast<int64_t>(b) * T * P.H + h) * K, offV = (static_cast<int64_t>(b) * T * P.H + h) * 64;
+    const int64_t offK = (static_cast<int64_t>(b) * P.T * P.H + h) * K, offV = (static_cast<int64_t>(b) * P.T * P.H + h) * 64;
     const __half *pa = P.g + offK, *pq = P.q + offK, *pk = P.k + offK, *px = P.d_o + offV;
     __half* pout = P.dv + offV;
 
-    float2 S[NC / 2];
+    float2 S[RC][2];
+    const float* init = P.nseg > 1 ? P.seg_state + ((static_cast<int64_t>(P.B) * P.H + bh) * P.nseg + seg) * K * 64
+                        : P.dht ? P.dht + static_cast<int64_t>(bh) * K * 64 : nullptr;
 #pragma unroll
-    for (int j = 0; j < NC / 2; ++j) {
-        const float* src = P.dht + (static_cast<int64_t>(bh) * K + part * NC + 2 * j) * 64 + col;
-        S[j] = P.dht ? make_float2(src[0], src[64]) : make_float2(0.f, 0.f);
+    for (int r = 0; r < RC; ++r) {
+        const int row = (r / 4) * 32 + 4 * rg + (r % 4);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+            S[r][c] = init ? *reinterpret_cast<const float2*>(init + row * 64 + 4 * cg + 2 * c) : make_float2(0.f, 0.f);
     }
 
-    const int nchunks = (T + kBwdChunk - 1) / kBwdChunk;
+    const int nchunks = (T - t_begin + kBwdChunk - 1) / kBwdChunk;
     uint4 ra[K / 32], rq[K / 32], rk[K / 32], rx[2];
     auto fetch = [&](int ci) {
-        const int t0 = (nchunks - 1 - ci) * kBwdChunk;
+        const int t0 = t_begin + (nchunks - 1 - ci) * kBwdChunk;
         bwd_fetch<K>(ra, pa, strideK, t0, T, tid);
         bwd_fetch<K>(rq, pq, strideK, t0, T, tid);
         bwd_fetch<K>(rk, pk, strideK, t0, T, tid);
@@ -257,35 +350,40 @@ __device__ void bwd_col_sweep(const BwdParams& P, BwdSmem& sm, int bh) {
     };
     if (nchunks > 0) fetch(0);
     for (int ci = 0; ci < nchunks; ++ci) {
-        const int t0 = (nchunks - 1 - ci) * kBwdChunk;
+        const int t0 = t_begin + (nchunks - 1 - ci) * kBwdChunk;
         bwd_spread<K, true>(sm.tile[0], ra, 1.f, tid);
         bwd_spread<K, false>(sm.tile[1], rq, P.scale, tid);
         bwd_spread<K, false>(sm.tile[2], rk, 1.f, tid);
         bwd_spread<64, false>(sm.tile[3], rx, 1.f, tid);
         __syncthreads();
         if (ci + 1 < nchunks) fetch(ci + 1);
-#pragma unroll 2
+#pragma unroll 4
         for (int tt = 0; tt < kBwdChunk; ++tt) {
             const int t = kBwdChunk - 1 - tt;
-            const float x = sm.tile[3][t * 64 + col];
-            const float4* A = reinterpret_cast<const float4*>(&sm.tile[0][t * K + part * NC]);
-            const float4* Q = reinterpret_cast<const float4*>(&sm.tile[1][t * K + part * NC]);
-            const float4* Kk = reinterpret_cast<const float4*>(&sm.tile[2][t * K + part * NC]);
-            const float2 xx = make_float2(x, x);
-            float2 acc2 = make_float2(0.f, 0.f);
+            float a[RC], qq[RC], kk[RC], x[4];
 #pragma unroll
-            for (int j = 0; j < NC / 4; ++j) {
-                const float4 a = A[j], qq = Q[j], kk = Kk[j];
-                S[2 * j] = bwd_fma2(make_float2(qq.x, qq.y), xx, S[2 * j]);
-                S[2 * j + 1] = bwd_fma2(make_float2(qq.z, qq.w), xx, S[2 * j + 1]);
-                acc2 = bwd_fma2(S[2 * j], make_float2(kk.x, kk.y), acc2);
-                acc2 = bwd_fma2(S[2 * j + 1], make_float2(kk.z, kk.w), acc2);
-                S[2 * j] = bwd_mul2(S[2 * j], make_float2(a.x, a.y));
-                S[2 * j + 1] = bwd_mul2(S[2 * j + 1], make_float2(a.z, a.w));
+            for (int i = 0; i < RC / 4; ++i) {
+                bwd_lds<4>(reinterpret_cast<float(&)[4]>(a[4 * i]), &sm.tile[0][t * K + 32 * i + 4 * rg]);
+                bwd_lds<4>(reinterpret_cast<float(&)[4]>(qq[4 * i]), &sm.tile[1][t * K + 32 * i + 4 * rg]);
+                bwd_lds<4>(reinterpret_cast<float(&)[4]>(kk[4 * i]), &sm.tile[2][t * K + 32 * i + 4 * rg]);
             }
-            float acc = acc2.x + acc2.y;
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            if (part == 0) sm.out[t * 64 + col] = acc;
+            bwd_lds<4>(x, &sm.tile[3][t * 64 + 4 * cg]);
+            const float2 x2[2] = {make_float2(x[0], x[1]), make_float2(x[2], x[3])};
+            float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+            for (int r = 0; r < RC; ++r) {
+                const float2 q2 = make_float2(qq[r], qq[r]), k2 = make_float2(kk[r], kk[r]), a2 = make_float2(a[r], a[r]);
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    S[r][c] = bwd_fma2(q2, x2[c], S[r][c]);
+                    acc[c] = bwd_fma2(S[r][c], k2, acc[c]);
+                    S[r][c] = bwd_mul2(S[r][c], a2);
+                }
+            }
+            const float v[4] = {acc[0].x, acc[0].y, acc[1].x, acc[1].y};
+            int which;
+            const float sum = bwd_reduce8<4>(v, lane, which);
+            if (!(lane & 1)) sm.out[t * 64 + 4 * cg + which] = sum;
         }
         __syncthreads();
 #pragma unroll
@@ -308,10 +406,48 @@ __device__ void bwd_col_sweep(const BwdParams& P, BwdSmem& sm, int bh) {
 template <int K>
 __global__ void __launch_bounds__(kBwdThreads) gla_bwd_sweep_kernel(const BwdParams P) {
     __shared__ __align__(16) BwdSmem sm;
-    const int bh = blockIdx.x, kind = blockIdx.y;
-    if (kind == 0) bwd_row_sweep<K, 0>(P, sm, bh);
-    else if (kind == 1) bwd_row_sweep<K, 1>(P, sm, bh);
-    else bwd_col_sweep<K>(P, sm, bh);
+    const int bh = blockIdx.x / P.nseg, seg = blockIdx.x % P.nseg, kind = blockIdx.y;
+    if (kind == 0) bwd_row_sweep<K, 0, false>(P, sm, bh, seg);
+    else if (kind == 1) bwd_row_sweep<K, 1, false>(P, sm, bh, seg);
+    else bwd_col_sweep<K>(P, sm, bh, seg);
+}
+
+// Sequences cut into segments (few sequences, many tokens): every segment but the last in sweep order first runs alone
+// from a zero state (this kernel: S of segments 0 .. nseg-2 forward, dS of segments 1 .. nseg-1 backward) ...
+template <int K>
+__global__ void __launch_bounds__(kBwdThreads) gla_bwd_state_kernel(const BwdParams P) {
+    __shared__ __align__(16) BwdSmem sm;
+    const int bh = blockIdx.x / (P.nseg - 1), i = blockIdx.x % (P.nseg - 1);
+    if (blockIdx.y == 0) bwd_row_sweep<K, 0, true>(P, sm, bh, i);
+    else bwd_row_sweep<K, 1, true>(P, sm, bh, i + 1);
+}
+
+// ... then the segments' contributions are chained, S' = decay * S + own, into the state each segment starts from
+// (written over the contribution), which gla_bwd_sweep_kernel picks up.  blockIdx.y: 0 forward states, 1 backward.
+template <int K>
+__global__ void __launch_bounds__(256) gla_bwd_combine_kernel(const BwdParams P) {
+    const int bh = blockIdx.x, back = blockIdx.y, nseg = P.nseg;
+    const int64_t slot0 = (static_cast<int64_t>(back ? P.B * P.H : 0) + bh) * nseg;
+    float* st = P.seg_state + slot0 * K * 64;
+    const float* dec = P.seg_decay + slot0 * K;
+    const float* init = back ? P.dht : P.h0;
+    for (int e = threadIdx.x; e < K * 64; e += blockDim.x) {
+        const int row = e / 64;
+        float S = init ? init[static_cast<int64_t>(bh) * K * 64 + e] : 0.f;
+        if (!back) {
+            for (int j = 0; j < nseg; ++j) {
+                const float own = j < nseg - 1 ? st[static_cast<int64_t>(j) * K * 64 + e] : 0.f;
+                st[static_cast<int64_t>(j) * K * 64 + e] = S;
+                if (j < nseg - 1) S = fmaf(dec[j * K + row], S, own);
+            }
+        } else {
+            for (int j = nseg - 1; j >= 0; --j) {
+                const float own = j > 0 ? st[static_cast<int64_t>(j) * K * 64 + e] : 0.f;
+                st[static_cast<int64_t>(j) * K * 64 + e] = S;
+                if (j > 0) S = fmaf(dec[j * K + row], S, own);
+            }
+        }
+    }
 }
 
 // dg_t = sum_{s >= t} (q_s dq_s - k_s dk_s), per (batch, head, channel).  One CTA per (batch, head): 1024 / K slices

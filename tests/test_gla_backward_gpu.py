@@ -54,7 +54,8 @@ def _inputs(B, T, H, K, seed, gate=("ls", 0.0, 1.0, 16.0), states=False):
 
 
 @pytest.mark.parametrize("B,T,H,K", [(2, 1, 2, 64), (1, 31, 1, 64), (2, 32, 3, 64), (1, 33, 2, 64), (2, 100, 3, 64),
-                                     (1, 257, 2, 32), (1, 640, 2, 64), (3, 70, 2, 32)])
+                                     (1, 257, 2, 32), (1, 640, 2, 64), (3, 70, 2, 32),
+                                     (1, 1000, 2, 64), (1, 600, 2, 32), (1, 2048, 1, 64)])   # cut into 3, 2 and 8 segments
 @pytest.mark.parametrize("states", [False, True])
 def test_gradients_against_the_oracle(G, B, T, H, K, states):
     from oracle import gla_bwd_ref
