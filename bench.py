@@ -167,7 +167,7 @@ def more_cpu_baselines(budget_s=4.0):
     return out
 
 
-def fla_triton_comparator(timeout_s=200):
+def fla_triton_comparator(timeout_s=150, backward=False):
     """flash-linear-attention's Triton chunk_gla (what the reference falls back to at K = 64) on this GPU, c3 shape.
     Run in a child process with a time limit (a Triton build can take a while); context only, never the target."""
     code = r"""
@@ -185,6 +185,7 @@ e1.record(); torch.cuda.synchronize()
 us = e0.elapsed_time(e1) * 1000 / 20
 res = {'us_per_forward': us, 'tokens_per_s': q.shape[0] * q.shape[1] / (us * 1e-6), 'finite': bool(torch.isfinite(o).all())}
 print(json.dumps(res), flush=True)
+if not %r: sys.exit(0)
 leaves = [x.clone().requires_grad_(True) for x in (q, k, v, g)]
 do = torch.randn_like(v)
 def both():
@@ -197,15 +198,16 @@ for _ in range(10): both()
 e1.record(); torch.cuda.synchronize()
 res['us_forward_and_backward'] = e0.elapsed_time(e1) * 1000 / 10
 print(json.dumps(res), flush=True)
-""" % ROOT
+""" % (ROOT, bool(backward))
     try:
         run = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=timeout_s)
         lines = [l for l in run.stdout.strip().splitlines() if l.startswith("{")]
         if not lines:
             return {"unavailable": (run.stderr.strip().splitlines() or ["failed"])[-1][:200]}
         res = json.loads(lines[-1])          # the forward figure stands even if the backward leg fails to build
-        res["what"] = ("fla.ops.gla.chunk_gla (Triton), c3 shape, 20 forwards back to back, inputs L2-resident between calls; "
-                       "then 10 forward + backward pairs through its autograd")
+        res["what"] = "fla.ops.gla.chunk_gla (Triton), c3 shape, 20 forwards back to back, inputs L2-resident between calls"
+        if backward:
+            res["what"] += "; then 10 forward + backward pairs through its autograd"
         return res
     except subprocess.TimeoutExpired:
         return {"unavailable": f"no result within {timeout_s} s"}
@@ -635,7 +637,8 @@ def run_ours(args, rank, local_rank, world):
                 except Exception as e:
                     extra["gradient"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
                 extra["cpu_baselines"] = more_cpu_baselines()
-                extra["fla_triton_chunk_gla"] = fla_triton_comparator()
+                extra["fla_triton_chunk_gla"] = (fla_triton_comparator(400, backward=True) if args.fla_backward
+                                                 else fla_triton_comparator())
         tokens_per_step = B * T * inner
         value = world * tokens_per_step * args.steps / (total_ms * 1e-3)
         achieved = algo_bytes / (kern_us * 1e-6) / 1e9
@@ -682,6 +685,8 @@ def main():
                     help="run only the backbone leg (--backbone-batch, --backbone-steps) and exit (for ncu)")
     ap.add_argument("--profile-forwards", type=int, default=0,
                     help="run only warmup + N forwards of the workload (for ncu) and exit")
+    ap.add_argument("--fla-backward", action="store_true",
+                    help="also time the Triton comparator's forward + backward (its kernels take minutes to build)")
     ap.add_argument("--profile-backward", type=int, default=0,
                     help="run this many gradient calls (gla_b200_backward) on the workload after --warmup calls, then exit")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

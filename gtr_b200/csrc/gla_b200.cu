@@ -602,7 +602,7 @@ size_t gla_b200_backward_workspace_bytes(int32_t B, int32_t T, int32_t H, int32_
     const size_t per = align_up(static_cast<size_t>(B) * T * H * K * sizeof(float), 256);
     int seg_len = 0;
     const size_t nseg = static_cast<size_t>(bwd_segments(B, T, H, &seg_len));
-    const size_t seg = nseg > 1 ? align_up(2 * static_cast<size_t>(B) * H * nseg * K * (64 + 1) * sizeof(float), 256) : 0;
+    const size_t seg = nseg > 1 ? align_up(2 * static_cast<size_t>(B) * H * nseg * K * (2 * 64 + 1) * sizeof(float), 256) : 0;
     return 2 * per + align_up(static_cast<size_t>(B) * H * K * sizeof(float), 256) + seg;
 }
 
@@ -637,7 +637,8 @@ int gla_b200_backward(const gla_b200_bwd_args* a, void* stream_v) {
     P.nseg = bwd_segments(a->B, a->T, a->H, &P.seg_len);
     const size_t last = align_up(static_cast<size_t>(a->B) * a->H * a->K * sizeof(float), 256);
     P.seg_state = reinterpret_cast<float*>(ws + 2 * per + last);
-    P.seg_decay = P.seg_state + 2 * static_cast<size_t>(a->B) * a->H * P.nseg * a->K * 64;
+    P.seg_start = P.seg_state + 2 * static_cast<size_t>(a->B) * a->H * P.nseg * a->K * 64;
+    P.seg_decay = P.seg_start + 2 * static_cast<size_t>(a->B) * a->H * P.nseg * a->K * 64;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const unsigned bh = static_cast<unsigned>(a->B * a->H);
     if (static_cast<int64_t>(bh) * P.nseg > 0x7fffffffLL) return GLA_B200_ERR_SHAPE;
@@ -645,10 +646,11 @@ int gla_b200_backward(const gla_b200_bwd_args* a, void* stream_v) {
     do {                                                                                                              \
         if (P.nseg > 1) {                                                                                             \
             gla::gla_bwd_state_kernel<KK><<<dim3(bh * (P.nseg - 1), 2), gla::kBwdThreads, 0, stream>>>(P);            \
-            gla::gla_bwd_combine_kernel<KK><<<dim3(bh, 2), 256, 0, stream>>>(P);                                      \
+            gla::gla_bwd_combine_kernel<KK><<<dim3(bh, 2, KK / 4), 256, 0, stream>>>(P);                                   \
         }                                                                                                             \
         gla::gla_bwd_sweep_kernel<KK><<<dim3(bh * P.nseg, 3), gla::kBwdThreads, 0, stream>>>(P);                      \
-        gla::gla_bwd_dg_kernel<KK><<<bh, 1024, 0, stream>>>(P);                                                       \
+        if (bh >= 256) gla::gla_bwd_dg_kernel<KK, KK><<<dim3(bh, 1), 1024, 0, stream>>>(P);                           \
+        else gla::gla_bwd_dg_kernel<KK, 16><<<dim3(bh, KK / 16), 1024, 0, stream>>>(P);                               \
     } while (0)
     if (a->K == 64) GLA_BWD_LAUNCH(64);
     else GLA_BWD_LAUNCH(32);

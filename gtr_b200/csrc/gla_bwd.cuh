@@ -34,7 +34,8 @@ struct BwdParams {
     float* dh0;           // [B,H,K,64] or null
     float *qdq, *kdk;     // scratch [B,T,H,K]
     float* g_last;        // scratch [B,H,K]: sum_v dht * final_state
-    float* seg_state;     // scratch [2][B*H][nseg][K,64]: a segment's own contribution, then the state it starts from
+    float* seg_state;     // scratch [2][B*H][nseg][K,64]: a segment's own contribution (forward S, backward dS)
+    float* seg_start;     // scratch, same shape: the state a segment starts from
     float* seg_decay;     // scratch [2][B*H][nseg][K]: product of the gates over a segment
     int B, T, H;
     int nseg, seg_len;    // a sequence is cut into nseg pieces of seg_len tokens (a multiple of 32), each its own CTA
@@ -170,7 +171,7 @@ __device__ void bwd_row_sweep(const BwdParams& P, BwdSmem& sm, int bh, int seg) 
     float2 S[R][4];
     float decay[R];
     const float* init = kStateOnly ? nullptr
-                        : P.nseg > 1 ? P.seg_state + seg_slot * K * 64 + block_off
+                        : P.nseg > 1 ? P.seg_start + seg_slot * K * 64 + block_off
                         : (kFwd ? P.h0 : P.dht) ? (kFwd ? P.h0 : P.dht) + state_off : nullptr;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -329,7 +330,7 @@ __device__ void bwd_col_sweep(const BwdParams& P, BwdSmem& sm, int bh, int seg) 
     __half* pout = P.dv + offV;
 
     float2 S[RC][2];
-    const float* init = P.nseg > 1 ? P.seg_state + ((static_cast<int64_t>(P.B) * P.H + bh) * P.nseg + seg) * K * 64
+    const float* init = P.nseg > 1 ? P.seg_start + ((static_cast<int64_t>(P.B) * P.H + bh) * P.nseg + seg) * K * 64
                         : P.dht ? P.dht + static_cast<int64_t>(bh) * K * 64 : nullptr;
 #pragma unroll
     for (int r = 0; r < RC; ++r) {
@@ -423,55 +424,63 @@ __global__ void __launch_bounds__(kBwdThreads) gla_bwd_state_kernel(const BwdPar
 }
 
 // ... then the segments' contributions are chained, S' = decay * S + own, into the state each segment starts from
-// (written over the contribution), which gla_bwd_sweep_kernel picks up.  blockIdx.y: 0 forward states, 1 backward.
+// (seg_start, laid out like seg_state), which gla_bwd_sweep_kernel picks up.  blockIdx.y: 0 forward states, 1 backward;
+// one state element per thread, so the loads of a thread do not depend on one another.
 template <int K>
 __global__ void __launch_bounds__(256) gla_bwd_combine_kernel(const BwdParams P) {
     const int bh = blockIdx.x, back = blockIdx.y, nseg = P.nseg;
+    const int e = blockIdx.z * 256 + threadIdx.x, row = e / 64;
     const int64_t slot0 = (static_cast<int64_t>(back ? P.B * P.H : 0) + bh) * nseg;
-    float* st = P.seg_state + slot0 * K * 64;
-    const float* dec = P.seg_decay + slot0 * K;
+    const float* __restrict__ own = P.seg_state + slot0 * K * 64 + e;
+    float* __restrict__ start = P.seg_start + slot0 * K * 64 + e;
+    const float* __restrict__ dec = P.seg_decay + slot0 * K + row;
     const float* init = back ? P.dht : P.h0;
-    for (int e = threadIdx.x; e < K * 64; e += blockDim.x) {
-        const int row = e / 64;
-        float S = init ? init[static_cast<int64_t>(bh) * K * 64 + e] : 0.f;
-        if (!back) {
-            for (int j = 0; j < nseg; ++j) {
-                const float own = j < nseg - 1 ? st[static_cast<int64_t>(j) * K * 64 + e] : 0.f;
-                st[static_cast<int64_t>(j) * K * 64 + e] = S;
-                if (j < nseg - 1) S = fmaf(dec[j * K + row], S, own);
-            }
-        } else {
-            for (int j = nseg - 1; j >= 0; --j) {
-                const float own = j > 0 ? st[static_cast<int64_t>(j) * K * 64 + e] : 0.f;
-                st[static_cast<int64_t>(j) * K * 64 + e] = S;
-                if (j > 0) S = fmaf(dec[j * K + row], S, own);
-            }
+    float S = init ? init[static_cast<int64_t>(bh) * K * 64 + e] : 0.f;
+    if (!back) {
+#pragma unroll 4
+        for (int j = 0; j < nseg - 1; ++j) {
+            start[static_cast<int64_t>(j) * K * 64] = S;
+            S = fmaf(__ldg(dec + j * K), S, __ldg(own + static_cast<int64_t>(j) * K * 64));
         }
+        start[static_cast<int64_t>(nseg - 1) * K * 64] = S;
+    } else {
+#pragma unroll 4
+        for (int j = nseg - 1; j > 0; --j) {
+            start[static_cast<int64_t>(j) * K * 64] = S;
+            S = fmaf(__ldg(dec + j * K), S, __ldg(own + static_cast<int64_t>(j) * K * 64));
+        }
+        start[0] = S;
     }
 }
 
-// dg_t = sum_{s >= t} (q_s dq_s - k_s dk_s), per (batch, head, channel).  One CTA per (batch, head): 1024 / K slices
-// of the sequence, each summed on its own first, then walked backwards from the total of the slices after it.
-template <int K>
+// dg_t = sum_{s >= t} (q_s dq_s - k_s dk_s), per (batch, head, channel).  One CTA per (batch, head, kCh channels):
+// 1024 / kCh slices of the sequence, each summed on its own first, then walked backwards from the total of the slices
+// after it.  kCh = K reads whole rows (many sequences); kCh = 16 gives four times the CTAs (few, long sequences).
+template <int K, int kCh>
 __global__ void __launch_bounds__(1024) gla_bwd_dg_kernel(const BwdParams P) {
-    constexpr int kSlices = 1024 / K;
-    __shared__ float total[kSlices][K];
+    constexpr int kSlices = 1024 / kCh;
+    __shared__ float total[kSlices][kCh];
     const int bh = blockIdx.x, b = bh / P.H, h = bh % P.H, T = P.T;
-    const int c = threadIdx.x % K, s = threadIdx.x / K;
+    const int cl = threadIdx.x % kCh, c = blockIdx.y * kCh + cl, s = threadIdx.x / kCh;
     const int64_t stride = static_cast<int64_t>(P.H) * K, off = (static_cast<int64_t>(b) * T * P.H + h) * K + c;
+    const float* __restrict__ pq = P.qdq + off;
+    const float* __restrict__ pk = P.kdk + off;
+    float* __restrict__ pg = P.dg + off;
     const int per = (T + kSlices - 1) / kSlices, lo = s * per, hi = min(T, lo + per);
     const float last = P.g_last ? P.g_last[static_cast<int64_t>(bh) * K + c] : 0.f;
     float sum = 0.f;
-    for (int t = lo; t < hi; ++t) sum += P.qdq[off + t * stride] - P.kdk[off + t * stride];
+#pragma unroll 8
+    for (int t = lo; t < hi; ++t) sum += __ldg(pq + t * stride) - __ldg(pk + t * stride);
     if (lo < T && hi == T) sum += last;
-    total[s][c] = sum;
+    total[s][cl] = sum;
     __syncthreads();
     float run = 0.f;
-    for (int j = s + 1; j < kSlices; ++j) run += total[j][c];
+    for (int j = s + 1; j < kSlices; ++j) run += total[j][cl];
     if (lo < T && hi == T) run += last;
+#pragma unroll 8
     for (int t = hi - 1; t >= lo; --t) {
-        run += P.qdq[off + t * stride] - P.kdk[off + t * stride];
-        P.dg[off + t * stride] = run;
+        run += __ldg(pq + t * stride) - __ldg(pk + t * stride);
+        pg[t * stride] = run;
     }
 }
 
