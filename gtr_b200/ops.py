@@ -237,14 +237,27 @@ def chunk_gla_backward(q, k, v, g, do, scale: Optional[float] = None, initial_st
     return dq, dk, dv, dg, dh0
 
 
+def _scan_order(direction: int, grid_hw, T: int, device) -> torch.Tensor:
+    """perm[p] = canonical (row-major) index of the token the scan reads at step p
+    (vit_adapter_spatial_swiglu.py:88-94: flip after every block, transpose the grid after odd ones)."""
+    hg, wg = (1, T) if grid_hw is None else (int(grid_hw[0]), int(grid_hw[1]))
+    idx = torch.arange(hg * wg, device=device).reshape(hg, wg)
+    if direction >= 2:
+        idx = idx.t()
+    perm = idx.reshape(-1)
+    return perm.flip(0) if direction & 1 else perm.contiguous()
+
+
 class _ChunkGLA(torch.autograd.Function):
     """`chunk_gla` with a gradient: forward and backward are both this library's kernels."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, initial_state, scale, output_final_state, offs, segments):
-        o, final = _chunk_gla_forward(q, k, v, g, scale, initial_state, output_final_state, offs, segments=segments)
+    def forward(ctx, q, k, v, g, initial_state, scale, output_final_state, offs, segments, direction, grid_hw,
+                gk_normalizer):
+        o, final = _chunk_gla_forward(q, k, v, g, scale, initial_state, output_final_state, offs, direction=direction,
+                                      grid_hw=grid_hw, gk_normalizer=gk_normalizer, segments=segments)
         ctx.save_for_backward(q, k, v, g, initial_state)
-        ctx.scale, ctx.offs = scale, offs
+        ctx.scale, ctx.offs, ctx.direction, ctx.grid_hw, ctx.gk_normalizer = scale, offs, direction, grid_hw, gk_normalizer
         if final is None:
             final = q.new_empty(0, dtype=torch.float32)
             ctx.mark_non_differentiable(final)
@@ -259,6 +272,16 @@ class _ChunkGLA(torch.autograd.Function):
         if d_final is not None:
             d_final = d_final.float().contiguous()
         do = do.to(torch.float16)
+        logits = None
+        if ctx.gk_normalizer > 0.0:          # the forward kernel turned raw logits into log-space gates itself
+            logits = g.float()
+            g = (torch.nn.functional.logsigmoid(logits) / ctx.gk_normalizer).to(torch.float16)
+        inverse = None
+        if ctx.direction != 0:               # the gradient kernels walk tokens in memory order: put them in scan order
+            perm = _scan_order(ctx.direction, ctx.grid_hw, q.shape[1], q.device)
+            inverse = torch.empty_like(perm)
+            inverse[perm] = torch.arange(perm.numel(), device=perm.device)
+            q, k, v, g, do = (x.index_select(1, perm) for x in (q, k, v, g, do))
         if ctx.offs is None:
             dq, dk, dv, dg, ds0 = chunk_gla_backward(q, k, v, g, do, ctx.scale, s0, d_final, want_s0)
         else:
@@ -272,7 +295,11 @@ class _ChunkGLA(torch.autograd.Function):
                 dq[:, a:b], dk[:, a:b], dv[:, a:b], dg[:, a:b] = part[:4]
                 if want_s0:
                     ds0[i:i + 1] = part[4]
-        return dq, dk, dv, dg.to(g.dtype), ds0, None, None, None, None
+        if inverse is not None:
+            dq, dk, dv, dg = (x.index_select(1, inverse) for x in (dq, dk, dv, dg))
+        if logits is not None:               # d logsigmoid(x) / dx = sigmoid(-x)
+            dg = dg * torch.sigmoid(-logits) / ctx.gk_normalizer
+        return dq, dk, dv, dg.to(ctx.saved_tensors[3].dtype), ds0, None, None, None, None, None, None, None
 
 
 def chunk_gla(q, k, v, g, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,
@@ -280,21 +307,19 @@ def chunk_gla(q, k, v, g, scale: Optional[float] = None, initial_state: Optional
               gk_normalizer: float = 0.0, segments: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """FLA-style call (vit_adapter.py:566-568): returns (o, final_state); `_chunk_gla_forward` documents the arguments.
     When gradients are enabled and an input requires one, the call is recorded for autograd and its backward runs
-    `chunk_gla_backward` -- as FLA's operator does for the reference in training.  That path serves the plain row-major
-    scan with log-space gates (what FLA's signature expresses); the scan directions and the raw-logit gate mode are
-    inference features."""
+    `chunk_gla_backward` -- as FLA's operator does for the reference in training.  The gradient kernels serve the
+    row-major scan with log-space gates (what FLA's signature expresses); for the other scan directions the backward
+    gathers the tokens into scan order around them, and for raw gate logits it applies logsigmoid's derivative."""
     tensors = [x for x in (q, k, v, g, initial_state) if x is not None]
     if not (torch.is_grad_enabled() and any(x.requires_grad for x in tensors)):
         return _chunk_gla_forward(q, k, v, g, scale, initial_state, output_final_state, cu_seqlens, direction=direction,
                                   grid_hw=grid_hw, gk_normalizer=gk_normalizer, segments=segments)
-    if _direction_id(direction) != 0 or gk_normalizer > 0.0:
-        raise RuntimeError("the gradient is implemented for direction 0 and log-space gates; apply logsigmoid and the "
-                           "token order in PyTorch around the call when training")
     B, T, H, K = q.shape
     if scale is None:
         scale = K ** -0.5
     offs = None if cu_seqlens is None else _sequence_bounds(cu_seqlens, B, T)
-    o, final = _ChunkGLA.apply(q, k, v, g, initial_state, float(scale), bool(output_final_state), offs, int(segments))
+    o, final = _ChunkGLA.apply(q, k, v, g, initial_state, float(scale), bool(output_final_state), offs, int(segments),
+                               _direction_id(direction), grid_hw, float(gk_normalizer))
     return o, (final if output_final_state else None)
 
 

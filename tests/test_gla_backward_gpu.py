@@ -24,7 +24,7 @@ def G():
 
 
 def _rel(ref, got):
-    ref, got = ref.double().cpu().flatten(), got.double().cpu().flatten()
+    ref, got = ref.detach().double().cpu().flatten(), got.detach().double().cpu().flatten()
     assert bool(torch.isfinite(got).all())
     return float((got - ref).norm() / ref.norm().clamp_min(1e-30))
 
@@ -153,6 +153,37 @@ def test_argument_errors(G):
     assert _lib.lib().gla_b200_backward(a, None) == -2
     a.K = 64
     assert _lib.lib().gla_b200_backward(a, None) == -1          # pointers missing
-    qd = q.cuda()
-    with pytest.raises(RuntimeError):                            # the scan directions have no gradient
-        G.chunk_gla(qd.requires_grad_(True), k.cuda(), v.cuda(), g.cuda(), direction=1)
+
+
+@pytest.mark.parametrize("direction", [1, 2, 3])
+def test_autograd_in_the_other_scan_directions(G, direction):
+    """The gradient of a column / reversed scan is the row-major gradient of the tokens gathered into scan order."""
+    from oracle import gla_bwd_ref, gla_ref
+    grid = (9, 14)
+    q, k, v, g, do, s0, dht = _inputs(2, grid[0] * grid[1], 2, 64, seed=30 + direction, states=True)
+    leaves = [x.cuda().requires_grad_(True) for x in (q, k, v, g, s0)]
+    o, hT = G.chunk_gla(*leaves[:4], initial_state=leaves[4], output_final_state=True, direction=direction, grid_hw=grid)
+    ((o.float() * do.cuda().float()).sum() + (hT * dht.cuda()).sum()).backward()
+    perm = gla_ref.scan_order(direction, *grid)
+    want = gla_bwd_ref.recurrent_gla_backward(q[:, perm], k[:, perm], v[:, perm], g[:, perm], do[:, perm],
+                                              initial_state=s0, d_final_state=dht)
+    for i, n in enumerate(("dq", "dk", "dv", "dg")):
+        back = torch.empty_like(want[i])
+        back[:, perm] = want[i]
+        assert _rel(back, leaves[i].grad) <= REL_HALF, n
+    assert _rel(want[4], leaves[4].grad) <= REL_FLOAT
+
+
+def test_autograd_with_raw_gate_logits(G):
+    """gk_normalizer > 0: the operator takes logits x and uses logsigmoid(x) / normalizer; dx = dg * sigmoid(-x) / normalizer."""
+    from oracle import gla_bwd_ref
+    q, k, v, _, do, _, _ = _inputs(1, 300, 2, 64, seed=40)
+    x = (torch.randn(1, 300, 2, 64, generator=torch.Generator().manual_seed(41)) * 2).half()
+    leaves = [t.cuda().requires_grad_(True) for t in (q, k, v, x)]
+    o, _ = G.chunk_gla(*leaves, gk_normalizer=16.0)
+    (o.float() * do.cuda().float()).sum().backward()
+    g = torch.nn.functional.logsigmoid(x.double()) / 16
+    want = gla_bwd_ref.recurrent_gla_backward(q, k, v, g, do)
+    dx = want[3] * torch.sigmoid(-x.double()) / 16
+    for i, (n, w) in enumerate(zip(("dq", "dk", "dv", "dx"), (want[0], want[1], want[2], dx))):
+        assert _rel(w, leaves[i].grad) <= 2e-3, n                 # the gates reach the gradient kernels rounded to fp16
