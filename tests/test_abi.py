@@ -124,3 +124,31 @@ def test_python_front_end_rejects_cpu_tensors():
         gtr_b200.chunk_gla_run(q, q, q, q, 0.125, torch.zeros(16), q)
     with pytest.raises(ValueError):
         gtr_b200.ops._direction_id("diagonal")
+
+
+def test_backward_args_struct_and_argument_checks(L):
+    """gla_b200_bwd_args as ctypes sees it: nine tensor pointers, three state pointers, workspace, sizes, scale."""
+    from gtr_b200 import _lib
+    assert ctypes.sizeof(_lib.BwdArgs) == 13 * 8 + 8 + 5 * 4 + 4
+    per = 4 * 6400 * 12 * 64 * 4
+    need = L.gla_b200_backward_workspace_bytes(4, 6400, 12, 64, 64)
+    assert need >= 2 * per + 4 * 12 * 64 * 4                  # the two product arrays and the last-token term
+    assert need <= 2 * per + (64 << 20)                       # plus per-segment states: a few MB
+    many = L.gla_b200_backward_workspace_bytes(32, 2048, 12, 64, 64)     # many sequences: no segments
+    assert many < 2 * (32 * 2048 * 12 * 64 * 4) + (1 << 20)
+    assert L.gla_b200_backward_workspace_bytes(4, 6400, 12, 48, 64) == 0
+    assert L.gla_b200_backward(None, None) == -1
+    a = _lib.BwdArgs()
+    a.B, a.T, a.H, a.K, a.V = 1, 64, 1, 64, 32
+    assert L.gla_b200_backward(ctypes.byref(a), None) == -2
+    a.V = 64
+    assert L.gla_b200_backward(ctypes.byref(a), None) == -1   # pointers missing
+    a.T = 0
+    assert L.gla_b200_backward(ctypes.byref(a), None) == 0    # an empty problem is a no-op
+    fake = 0x10000
+    a.T = 64
+    a.q = a.k = a.v = a.g = a.d_o = a.dq = a.dk = a.dv = a.dg = fake
+    a.q = fake + 2
+    assert L.gla_b200_backward(ctypes.byref(a), None) == -3   # misaligned
+    a.q = fake
+    assert L.gla_b200_backward(ctypes.byref(a), None) == -5   # no workspace
