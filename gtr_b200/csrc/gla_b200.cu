@@ -142,6 +142,31 @@ int auto_chunks_per_segment(int NT, int nseq, int slots, size_t workspace_bytes)
     return best_cps;
 }
 
+// Staggered plan for r = slots / nseq CTAs per sequence, 2 <= r < kMaxPlanSegments (gla::Params::plan): segment 0 of
+// `pre` x the length of the others, r equal ones after it.  `pre` is what a pre-pass chunk costs next to an output-pass
+// chunk while both kinds run side by side; measured on 100 chunks with three CTAs per sequence, the fastest splits are
+// 18 + 28 + 27 + 27 for the plain operator (and with raw gate logits, which cost both passes) and 14 + 29 + 29 + 28 with
+// the fused epilogue (which costs the output pass only).  In units of one chunk's output pass every CTA then works
+// (1 + pre) x the middle segments' length.  Returns that cost (plus one for the look-back), or a negative number when
+// the plan does not apply.
+constexpr double kPlanPrePassPlain = 0.68, kPlanPrePassGated = 0.48;
+double staggered_plan(int NT, int nseq, int slots, size_t workspace_bytes, double pre, int* seg_start, int* ns_out) {
+    const int r = nseq > 0 ? slots / nseq : 0;
+    if (r < 2 || r + 1 > gla::kMaxPlanSegments || NT < kMinAutoCps * (r + 1)) return -1.0;
+    if (ws_layout(static_cast<size_t>(nseq), static_cast<size_t>(r + 1)).total > workspace_bytes) return -1.0;
+    const double mid = NT / (r + pre);
+    int n0 = static_cast<int>(pre * mid + 0.5);
+    if (n0 < 1) n0 = 1;
+    const int rest = NT - n0;
+    seg_start[0] = 0;
+    seg_start[1] = n0;
+    for (int i = 0; i < r; ++i) seg_start[i + 2] = seg_start[i + 1] + rest / r + (i < rest % r ? 1 : 0);
+    *ns_out = r + 1;
+    const int longest = rest / r + (rest % r ? 1 : 0);
+    const double with_pass = (1.0 + pre) * longest, relay = n0 + (seg_start[r + 1] - seg_start[r]);
+    return (with_pass > relay ? with_pass : relay) + 1.0;
+}
+
 // ---- tensor maps ------------------------------------------------------------------------
 struct MapKey {
     const void* ptr[gla::kNumTensors];
@@ -449,10 +474,22 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     const int nseq = a->B * a->H;
     const int slots = gla::kCtasPerSm * di.sms;
     int cps;
+    int plan_start[gla::kMaxPlanSegments + 1] = {0}, plan_ns = 0;
+    bool plan = false;
     if (a->segments > 0) cps = a->segments;
-    else cps = auto_chunks_per_segment(NT, nseq, slots, a->workspace ? a->workspace_bytes : 0);
+    else {
+        const size_t have = a->workspace ? a->workspace_bytes : 0;
+        cps = auto_chunks_per_segment(NT, nseq, slots, have);
+        const int ns_u = (NT + cps - 1) / cps;
+        const long rounds = (static_cast<long>(nseq) * ns_u + slots - 1) / slots;
+        // what the slowest item of the equal split costs, in the plan's units: every segment but the last pays the pre-pass
+        const double pre = gated ? kPlanPrePassGated : kPlanPrePassPlain;
+        const double uniform_cost = rounds * (cps * (1.0 + (ns_u > 1 ? pre : 0.0)) + (ns_u > 1 ? 1.0 : 0.0));
+        const double plan_cost = staggered_plan(NT, nseq, slots, have, pre, plan_start, &plan_ns);
+        plan = plan_cost > 0.0 && plan_cost < uniform_cost;
+    }
     if (cps > NT) cps = NT;
-    const int NS = (NT + cps - 1) / cps;
+    const int NS = plan ? plan_ns : (NT + cps - 1) / cps;
     const WsLayout L = ws_layout(static_cast<size_t>(nseq), static_cast<size_t>(NS));
     if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < L.total)
         return GLA_B200_ERR_WORKSPACE;
@@ -468,6 +505,8 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     P.Hc = key.Hc; P.Wc = key.Wc;
     P.rev = a->direction & 1;
     P.NS = NS; P.cps = cps;
+    P.plan = plan ? 1 : 0;
+    for (int i = 0; i <= gla::kMaxPlanSegments; ++i) P.seg_start[i] = plan_start[i];
     P.num_items = nseq * NS;
     P.gated = gated ? 1 : 0;
     // q and k each carry sqrt(scale) / 4 (head-room for the gate factors in fp16); the 16 comes back in the epilogue

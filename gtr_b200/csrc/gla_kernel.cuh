@@ -105,6 +105,8 @@ struct Maps {
     CUtensorMap m[kNumTensors][kNumBoxes];
 };
 
+constexpr int kMaxPlanSegments = 16;
+
 struct Params {
     int B, T, H, NT;
     int K;               // key channels per head, 32 or 64.  A K = 32 head runs as a K = 64 head whose upper 32
@@ -114,6 +116,13 @@ struct Params {
     int Hc, Wc;          // column length / number of columns of the scan (row scans: Hc = T, Wc = 1)
     int rev;             // scan runs from the last token to the first
     int NS, cps;         // segments per sequence, chunks per segment
+    // Staggered plan (plan != 0; few sequences): NS = r + 1 segments of unequal length for r CTAs per sequence.  Segment
+    // 0 is short, runs its output pass at once (its start state is the call's initial state) and publishes the state
+    // after it; segments 1 .. r-1 run a pre-pass meanwhile, which takes as long when they are twice as long; the last
+    // segment needs no pre-pass and is taken by whichever CTA is free first -- so only r - 1 of r + 1 segments are read
+    // twice, and nobody waits.  seg_start[s] is the first chunk of segment s, seg_start[NS] = NT.
+    int plan;
+    int seg_start[kMaxPlanSegments + 1];
     int num_items;
     int gated;           // fused RMSNorm * w * silu(gate) epilogue
     // The output scale is folded into the exponents of the gate factors (q_exp = log2(scale), half of it on q and half
@@ -155,7 +164,11 @@ struct Misc {
     // ahead are rings indexed like the resource they guard (stage, team, or accumulator / tile pair).
     uint64_t ops_ready[kNumStages], g_ready[kNumStages];
     uint64_t x_done[kTeams], x_free[kTeams], a_done[kTeams], o_done[kTeams];
-    uint64_t inc_done[2], inc_free[2], s16_ready[2], s16_free[2];
+    // inc_free and s16_ready are waited for by the three teams in turn, each of which comes back to them only every
+    // third chunk: as rings of two they could be a whole phase behind a fast team (seen once the state group fell two
+    // chunks behind while a chunk's tiles came in late), and a wait that is two phases off passes at once.  Rings of
+    // four, indexed by the chunk, leave every waiter at most one phase from its barrier.
+    uint64_t inc_done[2], inc_free[4], s16_ready[4], s16_free[2];
     uint32_t tmem_base;
     volatile uint32_t abort;
     int item;
@@ -485,6 +498,7 @@ __global__ void wait_timeout_selftest_kernel(Params P) {
 
 struct ItemInfo {
     int seq, seg, b, h, first_chunk, nchunks, state_pass;
+    int publish_end;     // the state after the segment's output pass is what its successors start from
 };
 
 __device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
@@ -494,9 +508,17 @@ __device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
     it.seq = item - it.seg * nseq;
     it.b = it.seq / P.H;
     it.h = it.seq - it.b * P.H;
-    it.first_chunk = it.seg * P.cps;
-    it.nchunks = min(P.cps, P.NT - it.first_chunk);
-    it.state_pass = (it.seg < P.NS - 1) ? 1 : 0;
+    if (P.plan) {
+        it.first_chunk = P.seg_start[it.seg];
+        it.nchunks = P.seg_start[it.seg + 1] - it.first_chunk;
+        it.state_pass = (it.seg > 0 && it.seg < P.NS - 1) ? 1 : 0;
+        it.publish_end = (it.seg == 0 && P.NS > 1) ? 1 : 0;
+    } else {
+        it.first_chunk = it.seg * P.cps;
+        it.nchunks = min(P.cps, P.NT - it.first_chunk);
+        it.state_pass = (it.seg < P.NS - 1) ? 1 : 0;
+        it.publish_end = 0;
+    }
     return it;
 }
 
@@ -575,9 +597,11 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&M.inc_done[b]), 1);
+            mbar_init(smem_u32(&M.s16_free[b]), 1);
+        }
+        for (int b = 0; b < 4; ++b) {
             mbar_init(smem_u32(&M.inc_free[b]), kStateWarps);
             mbar_init(smem_u32(&M.s16_ready[b]), kStateWarps);
-            mbar_init(smem_u32(&M.s16_free[b]), 1);
         }
         M.abort = 0;
         fence_mbar_init();
@@ -762,7 +786,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         mbar_wait(ctx, &M.s16_free[j], ((c2 >> 1) & 1u) ^ 1u);
                         store_row_f16<4>(base + kOffS16 + j * kTileBytes, rho, 4u * hf, S);
                         fence_proxy_async_smem();
-                        warp_arrive(&M.s16_ready[j], l);
+                        warp_arrive(&M.s16_ready[c2 & 3u], l);
                     }
                 }
                 for (int i = 0; i < it.nchunks; ++i, ++ctr) {
@@ -802,14 +826,14 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     }
                     GLA_EV(51);
                     tc_fence_before();
-                    warp_arrive(&M.inc_free[p], l);
+                    warp_arrive(&M.inc_free[ctr & 3u], l);
                     if (!state_only) {
                         if (has_next) {
                             const uint32_t cn2 = c2 + 1, j = cn2 & 1u;
                             mbar_wait(ctx, &M.s16_free[j], ((cn2 >> 1) & 1u) ^ 1u);
                             store_row_f16<4>(base + kOffS16 + j * kTileBytes, rho, 4u * hf, S);
                             fence_proxy_async_smem();
-                            warp_arrive(&M.s16_ready[j], l);
+                            warp_arrive(&M.s16_ready[cn2 & 3u], l);
                         }
                         ++c2;
                     }
@@ -836,6 +860,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                     }
                 }
             }
+            if (it.publish_end) publish(P.incl + slot * (kD * kD) + hoff, 2u);
             if (it.seg == P.NS - 1 && P.sT != nullptr && real_row) {
                 float4* dst = reinterpret_cast<float4*>(P.sT + srow);
 #pragma unroll
@@ -918,7 +943,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                         fence_proxy_async_smem();
                         named_bar_sync(bar_id, kTeamThreads);
                         if (issuer) {
-                            mbar_wait(ctx, &M.inc_free[p], ((ctr >> 1) & 1u) ^ 1u);    // state group has read this buffer's previous use
+                            if (ctr >= 2u) mbar_wait(ctx, &M.inc_free[(ctr - 2u) & 3u], ((ctr - 2u) >> 2) & 1u);    // state group has read this buffer's previous use
                             tc_fence_after();
                             if (elect_one()) {
                                 const uint64_t dk = umma_desc_sw128(tk, 8192), dv = umma_desc_sw128(stage + 3 * kTileBytes, 8192);
@@ -988,7 +1013,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             umma_commit(smem_u32(&M.a_done[team]));      // exact path: the team wrote the accumulator itself
                         }
                         __syncwarp();
-                        mbar_wait(ctx, &M.inc_free[p], ((ctr >> 1) & 1u) ^ 1u);        // state group has read this buffer's previous use
+                        if (ctr >= 2u) mbar_wait(ctx, &M.inc_free[(ctr - 2u) & 3u], ((ctr - 2u) >> 2) & 1u);        // state group has read this buffer's previous use
                         tc_fence_after();
                         if (elect_one()) {
                             const uint64_t dk = umma_desc_sw128(tk, 8192), dv = umma_desc_sw128(stage + 3 * kTileBytes, 8192);
@@ -1036,7 +1061,7 @@ gla_fwd_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Params
                             for (uint32_t ks = 0; ks < 4; ++ks) umma_f16(tmT, da16 + ks * 2u, dv + ks * 128u, idO, ks);
                         }
                         __syncwarp();
-                        mbar_wait(ctx, &M.s16_ready[j], (k2 >> 1) & 1u);
+                        mbar_wait(ctx, &M.s16_ready[k2 & 3u], (k2 >> 2) & 1u);
                         tc_fence_after();
                         if (elect_one()) {
                             const uint64_t dq = umma_desc_sw128(tq), dS16 = umma_desc_sw128(base + kOffS16 + j * kTileBytes, 8192);
