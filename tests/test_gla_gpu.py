@@ -586,6 +586,23 @@ def test_staggered_segment_plans(G, B, H, T, direction, grid, K):
     assert (got - again).abs().max().item() <= 1e-3 * ref.abs().max().item()
 
 
+def test_many_launches_never_reach_the_wait_limit(G):
+    """The barrier protocol under the timing the staggered plan creates (pre-passes next to output passes, tiles that
+    come in late): 3000 launches of the benchmark's shape, the status word read after every one.  With two-deep rings
+    for the barriers the three teams share, about one launch in a hundred ran into the bounded waits here."""
+    from oracle import gla_ref
+    q, k, v, g = (x.cuda() for x in gla_ref.config_inputs("c3"))
+    B, T, H, _ = q.shape
+    ws = G.make_workspace(B, T, H, "cuda")
+    o = torch.empty(B, T, H, 64, dtype=torch.float16, device="cuda")
+    status = ws.view(torch.int32)
+    sets = [(q, k, v, g), tuple(x.clone() for x in (q, k, v, g))]
+    for it in range(3000):
+        G.chunk_gla_run(*sets[it % 2], 0.125, ws, o, direction=it % 4, grid_hw=(80, 80), wait_limit=100000)
+        torch.cuda.synchronize()
+        assert int(status[1]) == 0, f"launch {it}: a bounded wait expired (status {int(status[1])})"
+
+
 def test_packed_variable_length_sequences(G):
     """cu_seqlens (the FLA convention the reference block passes through): one row, sequences back to back."""
     from oracle import c_oracle, gla_ref
