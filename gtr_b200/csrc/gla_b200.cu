@@ -167,6 +167,23 @@ double staggered_plan(int NT, int nseq, int slots, size_t workspace_bytes, doubl
     return (with_pass > relay ? with_pass : relay) + 1.0;
 }
 
+// Relay plan (gla::Params::plan == 2) for more sequences than CTAs: the number of equal segments, without pre-passes,
+// that minimises rounds x (segment length + one chunk's worth of look-back); 1 when whole sequences are as good.
+int relay_segments(int NT, int nseq, int slots, size_t workspace_bytes, double* cost_out) {
+    int best = 1;
+    double best_cost = static_cast<double>((nseq + slots - 1) / slots) * NT;
+    for (int ns = 2; ns <= 8; ++ns) {
+        const int cps = (NT + ns - 1) / ns;
+        if (cps < kMinAutoCps || (NT + cps - 1) / cps != ns) continue;
+        if (ws_layout(static_cast<size_t>(nseq), static_cast<size_t>(ns)).total > workspace_bytes) continue;
+        const long rounds = (static_cast<long>(nseq) * ns + slots - 1) / slots;
+        const double cost = rounds * (cps + 1.0);
+        if (cost < best_cost * 0.97) { best_cost = cost; best = ns; }       // only for a gain worth the extra state traffic
+    }
+    *cost_out = best_cost;
+    return best;
+}
+
 // ---- tensor maps ------------------------------------------------------------------------
 struct MapKey {
     const void* ptr[gla::kNumTensors];
@@ -475,7 +492,7 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     const int slots = gla::kCtasPerSm * di.sms;
     int cps;
     int plan_start[gla::kMaxPlanSegments + 1] = {0}, plan_ns = 0;
-    bool plan = false;
+    bool plan = false, relay = false;
     if (a->segments > 0) cps = a->segments;
     else {
         const size_t have = a->workspace ? a->workspace_bytes : 0;
@@ -487,6 +504,11 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
         const double uniform_cost = rounds * (cps * (1.0 + (ns_u > 1 ? pre : 0.0)) + (ns_u > 1 ? 1.0 : 0.0));
         const double plan_cost = staggered_plan(NT, nseq, slots, have, pre, plan_start, &plan_ns);
         plan = plan_cost > 0.0 && plan_cost < uniform_cost;
+        if (!plan && 2 * nseq > slots) {
+            double relay_cost = 0.0;
+            const int ns_r = relay_segments(NT, nseq, slots, have, &relay_cost);
+            if (ns_r > 1 && relay_cost < 0.97 * uniform_cost) { relay = true; cps = (NT + ns_r - 1) / ns_r; }
+        }
     }
     if (cps > NT) cps = NT;
     const int NS = plan ? plan_ns : (NT + cps - 1) / cps;
@@ -505,7 +527,7 @@ int gla_b200_forward(const gla_b200_args* a, void* stream_v) {
     P.Hc = key.Hc; P.Wc = key.Wc;
     P.rev = a->direction & 1;
     P.NS = NS; P.cps = cps;
-    P.plan = plan ? 1 : 0;
+    P.plan = plan ? 1 : relay ? 2 : 0;
     for (int i = 0; i <= gla::kMaxPlanSegments; ++i) P.seg_start[i] = plan_start[i];
     P.num_items = nseq * NS;
     P.gated = gated ? 1 : 0;

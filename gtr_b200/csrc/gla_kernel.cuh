@@ -121,6 +121,11 @@ struct Params {
     // after it; segments 1 .. r-1 run a pre-pass meanwhile, which takes as long when they are twice as long; the last
     // segment needs no pre-pass and is taken by whichever CTA is free first -- so only r - 1 of r + 1 segments are read
     // twice, and nobody waits.  seg_start[s] is the first chunk of segment s, seg_start[NS] = NT.
+    // Relay plan (plan == 2; more sequences than CTAs): NS equal segments and no pre-pass at all.  Every segment but the
+    // last publishes the state after its output pass and its successor starts from that; items are handed out
+    // segment-major, so a segment's predecessor was taken a whole round of CTAs earlier and has finished by the time
+    // anybody asks for it.  The point is the tail: 384 sequences on 148 CTAs are 3 rounds of whole sequences but 2.7
+    // rounds' worth of fifths.
     int plan;
     int seg_start[kMaxPlanSegments + 1];
     int num_items;
@@ -508,7 +513,12 @@ __device__ __forceinline__ ItemInfo decode_item(const Params& P, int item) {
     it.seq = item - it.seg * nseq;
     it.b = it.seq / P.H;
     it.h = it.seq - it.b * P.H;
-    if (P.plan) {
+    if (P.plan == 2) {
+        it.first_chunk = it.seg * P.cps;
+        it.nchunks = min(P.cps, P.NT - it.first_chunk);
+        it.state_pass = 0;
+        it.publish_end = (it.seg < P.NS - 1) ? 1 : 0;
+    } else if (P.plan) {
         it.first_chunk = P.seg_start[it.seg];
         it.nchunks = P.seg_start[it.seg + 1] - it.first_chunk;
         it.state_pass = (it.seg > 0 && it.seg < P.NS - 1) ? 1 : 0;

@@ -567,10 +567,14 @@ def test_work_decompositions(G, B, H, T, direction, grid):
     (1, 70, 64 * 13, 1, None, 64),             # two CTAs per sequence: three segments, reversed
     (4, 12, 15 * 87, 2, (15, 87), 32),         # three CTAs per sequence, K = 32, ragged column scan (T = 1305)
     (1, 37, 64 * 24, 0, None, 64),             # four CTAs per sequence
+    (13, 12, 2078, 1, None, 64),               # more sequences than CTAs: two relayed halves, no pre-pass, reversed
+    (10, 16, 48 * 48, 3, (48, 48), 32),        # the same in thirds, K = 32, reversed column scan
+    (8, 12, 64 * 30 + 7, 0, None, 64),         # 96 sequences: the second and third thirds wait for the first
 ])
 def test_staggered_segment_plans(G, B, H, T, direction, grid, K):
     """Few sequences: a short first segment that runs at once and hands its state on, pre-passed middle segments, a
-    last segment taken by the first free CTA (automatic segmentation), with incoming and outgoing states."""
+    last segment taken by the first free CTA.  Many sequences: equal segments that hand their state on, no pre-pass.
+    (Automatic segmentation, with incoming and outgoing states.)"""
     from oracle import c_oracle, gla_ref
     q, k, v, g = gla_ref.make_inputs(B, T, H, K=K, seed=B + T + K)
     s0 = torch.randn(B, H, K, 64, generator=torch.Generator().manual_seed(T)) * 0.5
